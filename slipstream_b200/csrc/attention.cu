@@ -15,15 +15,15 @@ extern "C" int ss_attn_simt(const void* q, int64_t q_stride, void* out, int64_t 
                             const int32_t* tile_req, const int32_t* tile_q0, int n_tiles,
                             const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                             int page_size, int64_t num_pages, float scale, int window, int dtype,
-                            const void* gate, int* err, cudaStream_t stream, float softcap) {
+                            const void* gate, int* err, cudaStream_t stream, float softcap, const float* sinks) {
     if (n_tiles <= 0) return 0;
     if (dtype == SS_BF16)
         return launch_attn_simt<bf16, HEAD_DIM>(q, q_stride, out, out_stride, kv, block_tables, max_blocks,
                                                 tile_req, tile_q0, n_tiles, q_start, seq_lens, n_q, n_kv,
-                                                page_size, num_pages, scale, window, gate, err, stream, softcap);
+                                                page_size, num_pages, scale, window, gate, err, stream, softcap, sinks);
     return launch_attn_simt<float, HEAD_DIM>(q, q_stride, out, out_stride, kv, block_tables, max_blocks,
                                              tile_req, tile_q0, n_tiles, q_start, seq_lens, n_q, n_kv,
-                                             page_size, num_pages, scale, window, gate, err, stream, softcap);
+                                             page_size, num_pages, scale, window, gate, err, stream, softcap, sinks);
 }
 
 #include "attention_mma.cuh"
@@ -39,7 +39,7 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
                                    const int32_t* tile_req, const int32_t* tile_row0, int n_tiles,
                                    const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                    int page_size, int64_t num_pages, float scale, int window, const void* gate, int* err,
-                                   cudaStream_t stream, float softcap) {
+                                   cudaStream_t stream, float softcap, const float* sinks) {
     if (n_tiles <= 0) return 0;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>();
     static SsPerDevice opted;
@@ -47,14 +47,15 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
     dim3 grid(n_tiles, n_kv);
     ss_launch(attn_prefill_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, tile_req,
-        tile_row0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const bf16*)gate, softcap);
+        tile_row0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const bf16*)gate, softcap, sinks);
     return SS_LAUNCH_CHECK();
 }
 
 // Requests that bring one token each, bfloat16, split over the keys into n_slices.  part_o
 // ([requests][n_q][n_slices][D] float32), part_lse ([requests][n_q][n_slices] float32) and counters (one int
 // per request and block of 16 heads of a kv group; zero before the first call, left zero by every call) are
-// scratch memory of the caller; they are not touched when n_slices is at most 8.  fused: q points at rows
+// scratch memory of the caller; they are not touched when n_slices is at most 8.  sinks (here and in the two entry
+// points above; float32, one per query head, or null): one more term exp(sinks[h]) in the softmax's denominator.  fused: q points at rows
 // [q heads | k heads | v heads] as projected; the kernel rotates queries and the newest key by the request's
 // last position (inv_freq: float32 [rot_dim / 2]) and writes the newest key and value to their page.
 extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
@@ -62,7 +63,7 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
                                   const float* inv_freq, int rot_dim, int fused, float* part_o, float* part_lse, int* counters,
-                                  const void* gate, int* err, cudaStream_t stream, float softcap) {
+                                  const void* gate, int* err, cudaStream_t stream, float softcap, const float* sinks) {
     if (n_requests <= 0) return 0;
     const int cluster = n_slices >= 2 && n_slices <= 8;  // the slices are combined through shared memory
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
@@ -76,11 +77,11 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
     if (cluster)
         ss_launch_cluster(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, n_slices,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap, sinks);
     else
         ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap, sinks);
     return SS_LAUNCH_CHECK();
 }
 
@@ -257,7 +258,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, (const float*)nullptr, 0, 0, part_o, part_lse, counters, err, (const bf16*)nullptr, 0.f);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, (const float*)nullptr, 0, 0, part_o, part_lse, counters, err, (const bf16*)nullptr, 0.f, (const float*)nullptr);
     return SS_LAUNCH_CHECK();
 }
 

@@ -235,7 +235,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_row0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
                  int page_size, int64_t num_pages, float scale, int window, int* err, const bf16* __restrict__ gate,
-                 float softcap) {
+                 float softcap, const float* __restrict__ sinks) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int KSTR = D + 8;
@@ -277,6 +277,16 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
         pos2[h] = row < rows_here ? seq_len - q_len + (row0 + row) / G : -1;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (sinks) {  // one more term exp(sinks[head]) in each row's denominator (scores here are in units of log2 e)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = warp * 16 + (lane >> 2) + h * 8;
+            if (row < rows_here) {
+                m[h] = sinks[kvh * G + (row0 + row) % G] * 1.4426950408889634f;
+                l[h] = (lane & 3) == 0 ? 1.f : 0.f;  // l is summed over the four lanes of a row at the end
+            }
+        }
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -351,7 +361,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
                 int page_size, int64_t num_pages, float scale, int window, int n_slices, int cluster,
                 const float* __restrict__ inv_freq, int rot_dim, int fused,
                 float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err,
-                const bf16* __restrict__ gate, float softcap) {
+                const bf16* __restrict__ gate, float softcap, const float* __restrict__ sinks) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     // Until pdl_wait() below, only what no kernel of this step writes is touched: the lengths, the block
     // table, and keys and values at positions before the newest token (earlier steps wrote those).  The
@@ -376,6 +386,16 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
     const int kt_lo = kt_first + slice * per, kt_hi = min(kt_last, kt_lo + per - 1);
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (sinks && slice == 0 && warp == 0) {  // the sink's term counts once: in the first warp of the first slice
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + h * 8;
+            if (row < heads_here) {
+                m[h] = sinks[kvh * G + g0 + row] * 1.4426950408889634f;
+                l[h] = (lane & 3) == 0 ? 1.f : 0.f;
+            }
+        }
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;

@@ -9,7 +9,8 @@
 // the batch.  Rows see keys j with  p - window < j <= p  (p = the row's own index
 // in the request; window 0 = all earlier keys), which is the packed-index causal
 // rule of slipstream/models/layers/attention.py:46-51; scores are scaled after the
-// dot product and softmax is float32 as in :64-88.  Replaces the gather + eager
+// dot product and softmax is float32 as in :64-88.  `sinks` (float32, one per query head, or null): the softmax's
+// denominator also holds exp(sinks[h]), a term without key or value that is not scaled.  Replaces the gather + eager
 // loop of slipstream/kernels/attention_ref.py:68-89 and the Triton decode kernel
 // slipstream/kernels/triton_paged.py:97-206.
 //
@@ -35,7 +36,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_q0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                  int n_q, int n_kv, int page_size, int64_t num_pages, float scale, int window,
-                 int* err, const T* __restrict__ gate, float softcap) {
+                 int* err, const T* __restrict__ gate, float softcap, const float* __restrict__ sinks) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int DPL = (D + 31) / 32;
@@ -67,8 +68,9 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
 #pragma unroll
     for (int i = 0; i < ATT_RPW; ++i) {
         lowest[i] = key_floor(pos0 + w * ATT_RPW + i, window);
-        m[i] = -INFINITY;
-        l[i] = 0.f;
+        // a sink: one more term exp(sinks[h]) in the row's denominator, with no key and no value; it counts once
+        m[i] = sinks ? sinks[h] : -INFINITY;
+        l[i] = sinks ? 1.f : 0.f;
 #pragma unroll
         for (int c = 0; c < DPL; ++c) acc[i][c] = 0.f;
     }
@@ -181,7 +183,8 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
                      const int32_t* block_tables, int max_blocks, const int32_t* tile_req,
                      const int32_t* tile_q0, int n_tiles, const int32_t* q_start,
                      const int32_t* seq_lens, int n_q, int n_kv, int page_size, int64_t num_pages,
-                     float scale, int window, const void* gate, int* err, cudaStream_t stream, float softcap = 0.f) {
+                     float scale, int window, const void* gate, int* err, cudaStream_t stream, float softcap = 0.f,
+                     const float* sinks = nullptr) {
     static_assert(ATT_RPW == 4, "the kernel packs four rows per warp into a float4");
     constexpr int smem = att_simt_smem_bytes<D>();
     static SsPerDevice opted;
@@ -189,6 +192,6 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
     dim3 grid(n_tiles, n_q);
     ss_launch(attn_simt_kernel<T, D>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv, block_tables, max_blocks, tile_req,
-        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const T*)gate, softcap);
+        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const T*)gate, softcap, sinks);
     return SS_LAUNCH_CHECK();
 }

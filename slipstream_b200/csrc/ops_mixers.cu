@@ -155,7 +155,8 @@ extern "C" int ss_round_stream(const float* in, void* out, int64_t n, cudaStream
 // input(t - (T - 1 - j))), where inputs in front of the step's first row come from the request's state
 // [slot][T - 1][C] (float32; index T - 2 is the newest) and inputs in front of the request's first token are the
 // zeros a fresh state holds.  `fused_update`: every request brings one token and the thread that read the state
-// also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.
+// also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.  `plus_input`: the
+// result is input + (bias +) convolution with no activation instead (a convolution on a branch's input).
 #define CONV_MAX_TAPS 8
 #define CONV_ROWS 32
 // A thread takes one channel over CONV_ROWS consecutive rows and keeps the channel's last T - 1 inputs in
@@ -166,7 +167,7 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
                  const float* __restrict__ bias, float* __restrict__ state, T* __restrict__ out,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                  const int32_t* __restrict__ slots, int R, int n_rows, int C, int n_taps, int n_slots, int fused_update,
-                 int* err) {
+                 int* err, int plus_input) {
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -210,7 +211,7 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS; ++j)  // (no register array is indexed by a run-time value)
             if (j <= back) acc = fmaf(w[j], j < back ? x[j] : cur, acc);
-        out[(int64_t)row * C + c] = from_float<T>(silu_exact(acc));
+        out[(int64_t)row * C + c] = from_float<T>(plus_input ? cur + acc : silu_exact(acc));
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < back) x[j] = j + 1 < back ? x[j + 1] : cur;
@@ -230,7 +231,7 @@ conv_silu_bf16x8_kernel(const bf16* __restrict__ proj, int64_t stride, int col0,
                         const float* __restrict__ bias, float* __restrict__ state, bf16* __restrict__ out,
                         const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                         const int32_t* __restrict__ slots, int R, int n_rows, int C, int n_taps, int n_slots,
-                        int fused_update, int* err) {
+                        int fused_update, int* err, int plus_input) {
     pdl_wait();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     if (c >= C) return;
@@ -297,7 +298,7 @@ conv_silu_bf16x8_kernel(const bf16* __restrict__ proj, int64_t stride, int col0,
 #pragma unroll
                 for (int j = 0; j <= MAXB; ++j)
                     if (j <= back) acc = fmaf(w[e + d][j], j < back ? x[e + d][j < MAXB ? j : 0] : cur[e + d], acc);
-                o2[d] = silu_exact(acc);
+                o2[d] = plus_input ? cur[e + d] + acc : silu_exact(acc);
             }
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(o2[0], o2[1]);
             packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
@@ -342,7 +343,7 @@ conv_state_kernel(const T* __restrict__ proj, int64_t stride, int col0, float* _
 extern "C" int ss_conv_silu(const void* proj, int64_t stride, int col0, const float* taps, const float* bias, float* state,
                             void* out, const int32_t* q_start, const int32_t* seq_lens, const int32_t* slots, int R,
                             int n_rows, int C, int n_taps, int n_slots, int fused_update, int dtype, int* err,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int plus_input) {
     if (n_rows <= 0 || R <= 0) return 0;
     if (n_taps < 1 || n_taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
     const dim3 grid((n_rows + CONV_ROWS - 1) / CONV_ROWS, (C + 127) / 128);
@@ -350,13 +351,13 @@ extern "C" int ss_conv_silu(const void* proj, int64_t stride, int col0, const fl
         ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0) {
         const dim3 grid8((n_rows + CONV_ROWS - 1) / CONV_ROWS, (C / 8 + 127) / 128);
         ss_launch(conv_silu_bf16x8_kernel, grid8, dim3(128), 0, stream, (const bf16*)proj, stride, col0, taps, bias, state,
-                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err, plus_input);
     } else if (dtype == SS_BF16)
         ss_launch(conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, col0, taps, bias, state,
-                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err, plus_input);
     else
         ss_launch(conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, col0, taps, bias, state,
-                  (float*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+                  (float*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err, plus_input);
     if (!fused_update && n_taps > 1) {
         const dim3 grid2(R, (C + 127) / 128);
         if (dtype == SS_BF16)

@@ -85,9 +85,9 @@ class ModelRunner:
             pools = pool_sizes(layouts, page_sizes, tokens, max_num_seqs, self.max_model_len, step_tokens)
         self.cache = CacheManager(layouts, pools, page_sizes, max_num_seqs, self.max_model_len)
         self.num_pages = self.cache.num_pages
-        self.store = PagedStore(layouts, self.runtime.dtype, self.device, self.model.entry_state, max_num_seqs)
+        self.store = PagedStore(layouts, self.runtime.dtype, self.device, self.model.state_plan(), max_num_seqs)
         self.model.attach_store(self.store)
-        self.has_state = any(self.model.entry_state)
+        self.has_state = any(self.model.state_plan())
         self.steps_run = 0
         self.last_h2d_bytes = 0
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"

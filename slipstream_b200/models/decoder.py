@@ -64,6 +64,10 @@ class DecoderLM:
             out.append(self.position_encoding)
         return out
 
+    def state_plan(self) -> list[list[StateSpec]]:
+        """What the store allocates per slot: every entry's state, then the embedding's."""
+        return [*self.entry_state, self.embedding_state_specs]
+
     def weight_specs(self) -> list[WeightSpec]:
         specs: dict[str, WeightSpec] = {}
         for part in self.parts():
@@ -122,6 +126,8 @@ class DecoderLM:
             self.entry_group.append(g)
             self.entry_index.append(self.group_layouts[g].num_entries)
             self.group_layouts[g].num_entries += 1
+        # the state the embedding keeps per request: the store holds it behind the entries' own
+        self.embedding_state_specs = list(self.embedding.state_specs())
 
     # ------------------------------------------------------------------ binding
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
@@ -137,6 +143,7 @@ class DecoderLM:
             kv = store.kv[g][self.entry_index[pos]] if g >= 0 else None
             self.bindings.append(LayerBinding(kv=kv, group=g, writes_cache=entry.cache_of is None,
                                               state=store.state[pos]))
+        self.embedding_state = store.state[len(self.order)] if len(store.state) > len(self.order) else {}
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one step reads: every entry of the order reads its block's weights,
@@ -147,7 +154,7 @@ class DecoderLM:
     # ------------------------------------------------------------------ forward
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's tokens through the order; float32 logits [wanted rows, vocab]."""
-        residual = self.embedding.forward(ctx.token_ids)
+        residual = self.embedding.forward_step(ctx.token_ids, ctx, self.embedding_state)
         if self.position_encoding is not None:
             self.position_encoding.on_embedding(residual, ctx)
         pending = normed = None

@@ -63,7 +63,7 @@ _OPS_SIGNATURES = {
                       c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ss_round_stream": [c_void_p, c_void_p, c_int64, c_void_p],
     "ss_conv_silu": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_ssm_scan": [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -79,15 +79,29 @@ _OPS_SIGNATURES = {
                            c_void_p],
     "ss_turn_heads": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "ss_soft_cap": [c_void_p, c_int64, c_float, c_void_p],
+    "ss_embed_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                     c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "ss_matrix_cell": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_void_p, c_void_p],
+    "ss_cell_output": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float,
+                       c_int, c_void_p],
+    "ss_gated_recurrence": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int, c_void_p, c_void_p],
+    "ss_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
+    "ss_latent_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_void_p],
+    "ss_head_product": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_void_p],
 }
 
 _ATTN_SIGNATURES = {
     "ss_attn_simt": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_float],
+                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
     "ss_attn_prefill_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                            c_int, c_void_p, c_void_p, c_void_p, c_float],
+                            c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                             c_void_p, c_void_p, c_float],
@@ -96,7 +110,7 @@ _ATTN_SIGNATURES = {
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
 }
 
 _GEMM_SIGNATURES = {
@@ -142,7 +156,7 @@ def ops_library() -> ctypes.CDLL:
     lib = _state.get("ops")
     if lib is None:
         require_cuda()
-        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "ops_mixers.cu", "sampling.cu"])
+        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "ops_mixers.cu", "ops_cells.cu", "sampling.cu"])
         _declare(lib, _OPS_SIGNATURES)
         _state["ops"] = lib
     return lib  # type: ignore[return-value]
@@ -521,6 +535,13 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
     return out
 
 
+def _check_sinks(sinks: torch.Tensor | None, n_q: int) -> None:
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != n_q:
+            raise KernelError("sinks must hold one value per query head")
+
+
 def _gate_ptr(gate: torch.Tensor | None, q: torch.Tensor, q_stride: int) -> int | None:
     if gate is None:
         return None
@@ -533,7 +554,8 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                          block_tables: torch.Tensor, tile_req: torch.Tensor, tile_q0: torch.Tensor,
                          q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
                          head_dim: int, scale: float, window: int = 0, chunk: int = 0,
-                         gate: torch.Tensor | None = None, softcap: float = 0.0) -> None:
+                         gate: torch.Tensor | None = None, softcap: float = 0.0,
+                         sinks: torch.Tensor | None = None) -> None:
     """Causal grouped-query attention of the step's query rows over the pages (``window`` / ``chunk``: `key_span`).
     ``softcap`` c > 0 (in every attention entry point but the tcgen05 one): a scaled score s enters the softmax as
     ``c * tanh(s / c)``.
@@ -542,8 +564,11 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
 
     ``q`` points at the first query head of row 0; rows are ``q_stride`` elements apart.
     ``out`` is [N, n_q * D].  ``tile_req`` / ``tile_q0`` list tiles of 16 consecutive query tokens
-    of one request (request index, first token within the request's rows of this step)."""
+    of one request (request index, first token within the request's rows of this step).
+    ``sinks`` (in this entry point and the two mma.sync ones; float32 [n_q]): the softmax's denominator of head h also
+    holds ``exp(sinks[h])``, a term that has no key and no value and is not scaled."""
     _need(out, q.dtype, "attention output")
+    _check_sinks(sinks, n_q)
     _need(kv, q.dtype, "kv pages")
     for name, t in (("block_tables", block_tables), ("tile_req", tile_req), ("tile_q0", tile_q0),
                     ("q_start", q_start), ("seq_lens", seq_lens)):
@@ -554,7 +579,7 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                             tile_q0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                             n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
                             _code(q.dtype), _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream(),
-                            float(softcap or 0.0)),
+                            float(softcap or 0.0), _ptr(sinks)),
            "paged_attention_simt")
 
 
@@ -562,12 +587,13 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                             block_tables: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor,
                             q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                             scale: float, window: int = 0, chunk: int = 0, gate: torch.Tensor | None = None,
-                            softcap: float = 0.0) -> None:
+                            softcap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
     """bfloat16 tensor-core attention for prompt portions and mixed batches.  A tile is 64 consecutive
     rows of one request, a row being a (query token, head of the kv group) pair in token-major order:
     ``tile_req`` / ``tile_row0`` list (request index, first row)."""
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
+    _check_sinks(sinks, n_q)
     if q.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention kernels take bfloat16")
     for name, t in (("block_tables", block_tables), ("tile_req", tile_req), ("tile_row0", tile_row0),
@@ -579,7 +605,7 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                                    tile_row0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
                                    _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream(),
-                                   float(softcap or 0.0)),
+                                   float(softcap or 0.0), _ptr(sinks)),
            "paged_attention_prefill")
 
 
@@ -680,7 +706,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
                            rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None,
                            stages: int = 2, chunk: int = 0, gate: torch.Tensor | None = None,
-                           softcap: float = 0.0) -> None:
+                           softcap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
@@ -695,7 +721,8 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     ``tma``: the kernel whose tiles are moved by TMA (head size 64 or 128, pages of 8, 16, 32 or 64 tokens;
     the default where it fits), or the one that moves them with cp.async (every head and page size).
     ``stages``: 2 or 3 tiles in the ring of the TMA-fed kernel."""
-    fits = tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
+    fits = tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0) and sinks is None
+    _check_sinks(sinks, n_q)
     if tma is None:
         tma = fits
     elif tma and not fits:
@@ -737,7 +764,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     if tma:
         _check(lib.ss_attn_decode_tma(*args, int(stages), *tail), "paged_attention_decode")
     else:
-        _check(lib.ss_attn_decode_mma(*args, *tail), "paged_attention_decode")
+        _check(lib.ss_attn_decode_mma(*args, *tail, _ptr(sinks)), "paged_attention_decode")
 
 
 WIDE_CONTEXT = 8192  # from this many cached tokens a decode step of few requests may use more than 8 slices
@@ -792,7 +819,7 @@ def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
                     ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                     rope: tuple[torch.Tensor | None, int] | None = None, chunk: int = 0,
-                    gate: torch.Tensor | None = None, softcap: float = 0.0) -> None:
+                    gate: torch.Tensor | None = None, softcap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
     """Attention of the step's rows over the pages, choosing the kernel for the batch.
 
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
@@ -805,28 +832,31 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     and values not yet in their pages; the decode kernel does both.
 
     ``gate``: a view of ``qkv`` [N, n_q * D]; the output is multiplied by its sigmoid, inside the attention kernel
-    except behind the tcgen05 prefill kernel, where `sigmoid_gate` follows."""
+    except behind the tcgen05 prefill kernel, where `sigmoid_gate` follows.
+
+    ``sinks`` (float32 [n_q]): one more term ``exp(sinks[h])`` in the softmax's denominator of head h; such layers run the
+    CUDA-core kernel or the mma.sync kernels."""
     if rope is not None and not (qkv.dtype == torch.bfloat16 and ctx.is_decode_only):
         raise KernelError("only bfloat16 decode steps rotate inside the attention kernel")
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)
         paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
-                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap)
+                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap, sinks)
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
         static = ctx.extras.get("static_max_seq_len")  # fixed when the step is captured
         longest = static or ctx.max_seq_len
         wide = ctx.extras.get("decode_wide", False) if static else is_long_context(ctx.max_seq_len)
-        wide = bool(wide) and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
+        wide = bool(wide) and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0) and sinks is None
         slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or chunk or longest), wide,
                                sm_count(qkv.device))
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
-                               stages=DECODE_RING_STAGES, chunk=chunk, gate=gate, softcap=softcap)
+                               stages=DECODE_RING_STAGES, chunk=chunk, gate=gate, softcap=softcap, sinks=sinks)
         return
-    if tcgen05_prefill_fits(head_dim, n_q, n_kv, kv.shape[3]):
+    if sinks is None and tcgen05_prefill_fits(head_dim, n_q, n_kv, kv.shape[3]):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv, window or chunk)
         parts = ctx.extras.get(key)
@@ -840,7 +870,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
-                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap)
+                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap, sinks)
 
 
 # --------------------------------------------------------------------------- sampling
@@ -1439,12 +1469,13 @@ def round_stream(residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor
 
 
 def conv_silu(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, bias: torch.Tensor | None,
-              state: torch.Tensor, ctx) -> torch.Tensor:
+              state: torch.Tensor, ctx, plus_input: bool = False) -> torch.Tensor:
     """``silu`` of a causal convolution per channel over each request's tokens.  Channel c of a token is
     ``proj[row, col0 + c]``; ``taps`` float32 [channels, T] (the last column multiplies the current token);
     ``state`` float32 [slots, T - 1, channels] holds each request's last T - 1 inputs (zeros for a request that
     starts), is read for the tokens in front of the step and left holding the step's last inputs.  Returns
-    [N, channels] in the dtype of ``proj``."""
+    [N, channels] in the dtype of ``proj``.  ``plus_input``: the result is ``input + convolution`` with no activation
+    instead (a convolution laid over a branch's input)."""
     _need(proj, None, "projection")
     _need(taps, torch.float32, "taps")
     _need(state, torch.float32, "convolution state")
@@ -1461,7 +1492,7 @@ def conv_silu(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, 
                                       state.data_ptr(), out.data_ptr(), ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(),
                                       ctx.state_slots.data_ptr(), ctx.num_requests, n, channels, n_taps, state.shape[0],
                                       int(ctx.is_decode_only), _code(proj.dtype), error_word(proj.device).data_ptr(),
-                                      _stream()), "conv_silu")
+                                      _stream(), int(plus_input)), "conv_silu")
     if not ctx.is_decode_only and n_taps > 1:
         _launches[0] += 1  # the state's update is a launch of its own
     return out
@@ -1668,6 +1699,190 @@ def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+# --------------------------------------------------------------------------- recurrent cells, latent attention
+
+def embed_sum(token_ids: torch.Tensor, table: torch.Tensor, ctx, *, pair_table: torch.Tensor | None = None,
+              pair_hash: tuple[int, int, int] | None = None, last_token: torch.Tensor | None = None,
+              position_table: torch.Tensor | None = None, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """An embedding that is a sum of rows, float32 [N, hidden] (``copies`` > 1: [N, copies, hidden], every copy alike):
+    ``scale * table[token]``, plus ``pair_table[(previous * mul_prev + token * mul_cur) mod buckets]`` with
+    ``pair_hash`` = (buckets, mul_prev, mul_cur) and row ``buckets`` for a request's first token, plus
+    ``position_table[position]``.  The token in front of a step's first row is the request's state ``last_token``
+    (int32 [slots]), which the kernel leaves holding the step's last token."""
+    _need(token_ids, torch.int32, "token_ids")
+    _need(table, None, "embedding table")
+    n, (vocab, hidden) = token_ids.numel(), table.shape
+    buckets = mul_prev = mul_cur = 0
+    if pair_table is not None:
+        _need(pair_table, table.dtype, "pair table")
+        _need(last_token, torch.int32, "last_token")
+        buckets, mul_prev, mul_cur = (int(v) for v in pair_hash)
+        if buckets < 1 or tuple(pair_table.shape) != (buckets + 1, hidden):
+            raise KernelError("the pair table must be [buckets + 1, hidden]")
+    if position_table is not None:
+        _need(position_table, table.dtype, "position table")
+        if position_table.shape[1] != hidden:
+            raise KernelError("the position table must be [positions, hidden]")
+    out = torch.empty((n, hidden) if copies == 1 else (n, copies, hidden), dtype=torch.float32, device=table.device)
+    _check(ops_library().ss_embed_sum(token_ids.data_ptr(), ctx.positions.data_ptr(), table.data_ptr(), _ptr(pair_table),
+                                      _ptr(position_table), out.data_ptr(), _ptr(last_token), ctx.q_start.data_ptr(),
+                                      ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(), ctx.num_requests, n, hidden, vocab,
+                                      int(copies), buckets, mul_prev, mul_cur,
+                                      position_table.shape[0] if position_table is not None else 0,
+                                      last_token.shape[0] if last_token is not None else 0, float(scale), _code(table.dtype),
+                                      error_word(table.device).data_ptr(), _stream()), "embed_sum")
+    return out
+
+
+def matrix_cell(qkv: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor | None, bias_f: torch.Tensor | None, cap: float,
+                q_scale: float, memory: torch.Tensor, peak: torch.Tensor, ctx, heads: int, dim: int, vdim: int
+                ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The matrix-memory recurrence over each request's tokens, continued from and left in ``memory`` (float32
+    [slots, heads, vdim + 1, dim]: S column by column, the last column the normaliser n) and ``peak`` (float32
+    [slots, heads], the running maximum m, which starts at 0).  A row of ``qkv`` starts with [q: heads * dim |
+    k: heads * dim | v: heads * vdim]; ``gates`` float32 [N, >= 2 heads] holds the raw input and forget gates.  With
+    ``i = cap tanh((a + bias_i) / cap)`` and ``f = logsigmoid(cap tanh((b + bias_f) / cap))``:
+    ``m' = max(f + m, i)``, ``S <- exp(f + m - m') S + exp(i - m') k v^T``, n likewise with k alone.
+    Returns (``S^T (q_scale q)`` float32 [N, heads * vdim], ``n . (q_scale q)`` [N, heads], m [N, heads])."""
+    _need(qkv, None, "q, k and v")
+    _need(gates, torch.float32, "gates")
+    _need(memory, torch.float32, "memory")
+    _need(peak, torch.float32, "peak")
+    n = qkv.shape[0]
+    if qkv.shape[1] < heads * (2 * dim + vdim) or gates.shape[0] != n or gates.shape[1] < 2 * heads:
+        raise KernelError("matrix_cell: q, k, v or the gates have the wrong shape")
+    if tuple(memory.shape[1:]) != (heads, vdim + 1, dim) or tuple(peak.shape[1:]) != (heads,) or not 1 <= dim <= 256:
+        raise KernelError("matrix_cell: the memory must be [slots, heads, vdim + 1, dim] with dim <= 256, the peak [slots, heads]")
+    for b in (bias_i, bias_f):
+        if b is not None:
+            _need(b, torch.float32, "gate bias")
+    num = torch.empty((n, heads * vdim), dtype=torch.float32, device=qkv.device)
+    nq = torch.empty((n, heads), dtype=torch.float32, device=qkv.device)
+    peaks = torch.empty((n, heads), dtype=torch.float32, device=qkv.device)
+    _check(ops_library().ss_matrix_cell(qkv.data_ptr(), qkv.stride(0), gates.data_ptr(), gates.stride(0), _ptr(bias_i),
+                                        _ptr(bias_f), float(cap), float(q_scale), memory.data_ptr(), peak.data_ptr(),
+                                        num.data_ptr(), nq.data_ptr(), peaks.data_ptr(), ctx.q_start.data_ptr(),
+                                        ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(), ctx.num_requests, heads, dim, vdim,
+                                        memory.shape[0], _code(qkv.dtype), error_word(qkv.device).data_ptr(), _stream()),
+           "matrix_cell")
+    return num, nq, peaks
+
+
+def cell_output(num: torch.Tensor, nq: torch.Tensor, peaks: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor,
+                heads: int, vdim: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """The matrix-memory cell's output: ``o = num / (max(|nq|, exp(-m)) + 1e-6)``, every head of ``o`` divided by its root
+    mean square (``eps`` inside the root), times ``weight`` (float32 [heads * vdim]), times ``sigmoid(gate)`` (a view
+    [N, heads * vdim] in ``out_dtype`` with unit inner stride).  Returns [N, heads * vdim] in ``out_dtype``."""
+    for name, t in (("num", num), ("nq", nq), ("peaks", peaks), ("weight", weight)):
+        _need(t, torch.float32, name)
+    n = num.shape[0]
+    if gate.dtype != out_dtype or gate.stride(1) != 1 or tuple(gate.shape) != (n, heads * vdim) or weight.numel() != heads * vdim:
+        raise KernelError("cell_output: the gate or the weight has the wrong shape")
+    out = torch.empty((n, heads * vdim), dtype=out_dtype, device=num.device)
+    _check(ops_library().ss_cell_output(num.data_ptr(), nq.data_ptr(), peaks.data_ptr(), weight.data_ptr(), gate.data_ptr(),
+                                        gate.stride(0), out.data_ptr(), n, heads, vdim, float(eps), _code(out_dtype),
+                                        _stream()), "cell_output")
+    return out
+
+
+def gated_recurrence(proj: torch.Tensor, width: int, state: torch.Tensor, ctx, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """A gated recurrence per channel over each request's tokens, continued from and left in ``state`` (float32
+    [slots, width]).  A row of ``proj`` is [z | u | g], ``width`` each; ``bias`` (float32 [2 width]) is added to z and u
+    in float32.  ``z' = sigmoid(z)``; the candidate is ``u + 1/2`` where ``u >= 0`` and ``sigmoid(u)`` below;
+    ``S <- (1 - z') S + z' candidate``; returns ``S silu(g)`` [N, width] in the dtype of ``proj``."""
+    _need(proj, None, "projection")
+    _need(state, torch.float32, "state")
+    if bias is not None:
+        _need(bias, torch.float32, "gate biases")
+        if bias.numel() != 2 * width:
+            raise KernelError("gated_recurrence: the biases must hold 2 * width values")
+    if proj.shape[1] < 3 * width or tuple(state.shape[1:]) != (width,):
+        raise KernelError("gated_recurrence: the projection or the state has the wrong shape")
+    out = torch.empty((proj.shape[0], width), dtype=proj.dtype, device=proj.device)
+    _check(ops_library().ss_gated_recurrence(proj.data_ptr(), proj.stride(0), _ptr(bias), state.data_ptr(), out.data_ptr(),
+                                             ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
+                                             ctx.num_requests, width, state.shape[0], _code(proj.dtype),
+                                             error_word(proj.device).data_ptr(), _stream()), "gated_recurrence")
+    return out
+
+
+def xielu(x: torch.Tensor, a: float, b: float) -> torch.Tensor:
+    """In place: ``a x^2 + x / 2`` where ``x > 0``, ``b (exp(x) - 1 - x) + x / 2`` elsewhere."""
+    _need(x, None, "x")
+    _check(ops_library().ss_xielu(x.data_ptr(), x.data_ptr(), x.numel(), float(a), float(b), _code(x.dtype), _stream()), "xielu")
+    return x
+
+
+def latent_rows(down: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None, kv: torch.Tensor | None,
+                q_weight: torch.Tensor, kv_weight: torch.Tensor | None, inv_freq: torch.Tensor | None, mscale: float,
+                q_rank: int, kv_rank: int, rot_dim: int, eps: float) -> torch.Tensor:
+    """The latents of a latent-attention layer.  A row of ``down`` is [query latent: q_rank | key/value latent: kv_rank |
+    shared key part: rot_dim | ...].  Returns ``rmsnorm(query latent) * q_weight`` [N, q_rank]; with ``kv_rank`` > 0 the
+    key/value latent is normed likewise (``kv_weight``), the shared key part rotated by the row's position (pairs
+    (i, i + rot_dim / 2), angle ``position * inv_freq[i]``, cosines and sines times ``mscale``; ``inv_freq`` None: not
+    rotated), and the pages ``kv`` [pages, 2, 1, page_size, D] take the key row [rotated part | latent | zeros] and the
+    value row [latent | zeros] at ``slots``."""
+    _need(down, None, "down projection")
+    _need(positions, torch.int32, "positions")
+    _need(q_weight, torch.float32, "query latent's norm weight")
+    n = down.shape[0]
+    dp = page_size = pages = 0
+    if kv_rank > 0:
+        _need(kv, down.dtype, "kv pages")
+        _need(slots, torch.int32, "slots")
+        _need(kv_weight, torch.float32, "latent's norm weight")
+        if kv.dim() != 5 or kv.shape[1] != 2 or kv.shape[2] != 1 or kv.shape[4] < kv_rank + rot_dim:
+            raise KernelError("latent_rows: the pages must be [pages, 2, 1, page_size, D] with D >= kv_rank + rot_dim")
+        pages, page_size, dp = kv.shape[0], kv.shape[3], kv.shape[4]
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() != rot_dim // 2:
+            raise KernelError("inv_freq must hold rot_dim / 2 values")
+    if down.shape[1] < q_rank + (kv_rank + rot_dim if kv_rank > 0 else 0) or rot_dim % 2:
+        raise KernelError("latent_rows: the down projection is narrower than its parts, or rot_dim is odd")
+    cq = torch.empty((n, q_rank), dtype=down.dtype, device=down.device)
+    _check(ops_library().ss_latent_rows(down.data_ptr(), down.stride(0), positions.data_ptr(), _ptr(slots) if kv_rank > 0 else None,
+                                        q_weight.data_ptr(), _ptr(kv_weight), _ptr(inv_freq), float(mscale), cq.data_ptr(),
+                                        _ptr(kv) if kv_rank > 0 else None, n, q_rank, kv_rank, rot_dim, dp, page_size, pages,
+                                        float(eps), _code(down.dtype), error_word(down.device).data_ptr(), _stream()),
+           "latent_rows")
+    return cq
+
+
+def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, *, turn: int = 0,
+                 pad_to: int | None = None, positions: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None,
+                 mscale: float = 1.0, gates: torch.Tensor | None = None) -> torch.Tensor:
+    """A product per head: ``out[n, h, turn + o] = f * sum_i x[n, h, i] * weight[h, i, o]`` with ``weight`` [H, I, O], head h
+    of a row of ``x`` starting at column ``h * x_head`` and of ``out`` at ``h * out_head``; float32 accumulation in the
+    order of i.  ``turn`` > 0: the ``turn`` elements of x behind the I inputs are rotated by the row's position (pairs
+    (i, i + turn / 2), ``inv_freq`` None: copied) into ``out[n, h, :turn]``.  Columns from ``turn + O`` to ``pad_to`` are
+    zeroed.  ``gates`` (a view [N, H] in the dtype of x, unit inner stride): ``f = sigmoid(gates[n, h])``, else 1."""
+    _need(x, None, "x")
+    _need(weight, x.dtype, "weights per head")
+    _need(out, x.dtype, "output")
+    h, i, o = weight.shape
+    n = x.shape[0]
+    pad_to = turn + o if pad_to is None else int(pad_to)
+    if x.shape[1] < (h - 1) * x_head + i + turn or out.shape[1] < (h - 1) * out_head + pad_to or out.shape[0] != n:
+        raise KernelError("head_product: x or out is narrower than its heads")
+    if turn:
+        _need(positions, torch.int32, "positions")
+    gate_stride = scale_col = 0
+    gate_ptr = None
+    if gates is not None:
+        if gates.dtype != x.dtype or gates.stride(1) != 1 or tuple(gates.shape) != (n, h):
+            raise KernelError("head_product: gates must be a view [N, H] in the dtype of x")
+        gate_ptr, gate_stride = gates.data_ptr(), gates.stride(0)
+    else:
+        scale_col = -1
+    _check(ops_library().ss_head_product(x.data_ptr(), x.stride(0), int(x_head), weight.data_ptr(), out.data_ptr(),
+                                         out.stride(0), int(out_head), n, h, i, o, int(turn), pad_to, _ptr(positions),
+                                         _ptr(inv_freq), float(mscale), gate_ptr, gate_stride, scale_col, _code(x.dtype),
+                                         _stream()), "head_product")
+    return out
+
+
+
 def set_programmatic_launch(enabled: bool) -> None:
     """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
     libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if isinstance(key, str) and key.startswith("attn")]
@@ -1681,4 +1896,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "linear_hc_rmsnorm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
            "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "tcgen05_prefill_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library", "group_norm", "round_stream", "conv_silu", "ssm_scan", "router", "moe_experts", "moe_combine",
-           "norm_rope_cache", "turn_heads", "soft_cap"]
+           "norm_rope_cache", "turn_heads", "soft_cap", "embed_sum", "matrix_cell", "cell_output", "gated_recurrence", "xielu",
+           "latent_rows", "head_product"]

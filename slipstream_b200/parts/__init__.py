@@ -5,11 +5,13 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    StateSpec, WeightSpec)
 from .attention import PagedAttention
 from .block import BranchNormBlock, PreNormBlock
-from .embedding import LMHead, TokenEmbedding
-from .mlp import GatedFeedForward, SwiGLUFeedForward
+from .embedding import LMHead, SummedEmbedding, TokenEmbedding
+from .mlp import ActivatedFeedForward, GatedFeedForward, SwiGLUFeedForward
 from .experts import RoutedExperts
 from .norm import GroupRMSNorm, RMSNorm, StreamRounding
 from .state_space import StateSpaceMixer
+from .recurrent import ConvolvedInput, GatedRecurrenceMixer, MatrixMemoryMixer
+from .latent_attention import LatentAttention
 from .rotary import NoPositionEncoding, RotaryEncoding, YarnRotaryEncoding
 from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
 
@@ -18,4 +20,5 @@ __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS"
            "Runtime", "StateSpec", "WeightSpec", "PagedAttention", "PreNormBlock", "LMHead",
            "TokenEmbedding", "SwiGLUFeedForward", "GatedFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
            "HyperConnectionBlock", "StreamWrite", "BranchNormBlock", "GroupRMSNorm", "StreamRounding", "RoutedExperts",
-           "StateSpaceMixer"]
+           "StateSpaceMixer", "SummedEmbedding", "ActivatedFeedForward", "ConvolvedInput", "GatedRecurrenceMixer",
+           "MatrixMemoryMixer", "LatentAttention"]

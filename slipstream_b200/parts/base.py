@@ -233,6 +233,15 @@ class Embedding(Part):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def state_specs(self) -> list[StateSpec]:
+        """Fixed-size per-request state of the embedding itself (the token in front of a step, say)."""
+        return []
+
+    def forward_step(self, token_ids: torch.Tensor, ctx: "StepContext", state: dict[str, torch.Tensor]) -> torch.Tensor:
+        """``forward`` for an embedding that reads the step's positions or its own per-request ``state`` (the rows
+        of the slot pool that ``state_specs`` asked for).  The default needs neither."""
+        return self.forward(token_ids)
+
 
 class Head(Part):
     """Normalised rows of the stream (compute dtype [M, hidden]) into float32 logits [M, vocab_size].  A head

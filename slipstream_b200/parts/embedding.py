@@ -8,7 +8,7 @@ import torch
 
 from slipstream_b200 import ops
 
-from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, WeightSpec
+from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, StateSpec, WeightSpec
 
 
 @EMBEDDINGS.register("token_table")
@@ -36,6 +36,62 @@ class TokenEmbedding(Embedding):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return ops.embedding(token_ids, self.weight, scale=self.scale, copies=self.copies)
+
+
+@EMBEDDINGS.register("summed_tables")
+class SummedEmbedding(Embedding):
+    """An embedding that is a sum of rows of up to three tables, formed in float32:
+
+    * the token's row of the token table (times ``scale``);
+    * with ``pair_hash`` = (buckets, mul_prev, mul_cur): row ``(previous * mul_prev + token * mul_cur) mod buckets`` of
+      a table of ``buckets + 1`` rows, whose last row serves a request's first token.  The previous token of a step's
+      first row is per-request state (``last_token``, an int32 per slot), so a request may be cut anywhere;
+    * with ``positions``: row ``position`` of a learned table of that many rows (not scaled).
+
+    ``copies``: how many residual streams the model keeps (see `TokenEmbedding`).  ``names``: the checkpoint's tensor
+    names by role (token, pair, position)."""
+
+    cuda_graph_safe = True
+
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, *, scale: float = 1.0, copies: int = 1,
+                 pair_hash: tuple[int, int, int] | None = None, positions: int | None = None,
+                 names: dict[str, str] | None = None) -> None:
+        self.name = name
+        self.vocab_size = vocab_size
+        self.hidden_size = hidden_size
+        self.scale = float(scale)
+        self.copies = int(copies)
+        self.pair_hash = None if pair_hash is None else tuple(int(v) for v in pair_hash)
+        self.positions = None if positions is None else int(positions)
+        if self.pair_hash is not None and (self.pair_hash[0] < 1 or min(self.pair_hash[1:]) < 0):
+            raise ValueError("pair_hash is (buckets >= 1, mul_prev >= 0, mul_cur >= 0)")
+        self.names = {"token": f"{name}.weight", "pair": f"{name}.pair.weight", "position": f"{name}.position.weight"}
+        self.names.update(names or {})
+
+    def weight_specs(self) -> list[WeightSpec]:
+        specs = [WeightSpec(self.names["token"], (self.vocab_size, self.hidden_size))]
+        if self.pair_hash is not None:
+            specs.append(WeightSpec(self.names["pair"], (self.pair_hash[0] + 1, self.hidden_size)))
+        if self.positions is not None:
+            specs.append(WeightSpec(self.names["position"], (self.positions, self.hidden_size)))
+        return specs
+
+    def state_specs(self) -> list[StateSpec]:
+        return [StateSpec("last_token", (), torch.int32)] if self.pair_hash is not None else []
+
+    def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(weights, runtime)
+        self.weight = weights[self.names["token"]]
+        self.pair_table = weights[self.names["pair"]] if self.pair_hash is not None else None
+        self.position_table = weights[self.names["position"]] if self.positions is not None else None
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise RuntimeError(f"{self.name}: this embedding needs the step's positions and state (forward_step)")
+
+    def forward_step(self, token_ids: torch.Tensor, ctx, state: dict[str, torch.Tensor]) -> torch.Tensor:
+        return ops.embed_sum(token_ids, self.weight, ctx, pair_table=self.pair_table, pair_hash=self.pair_hash,
+                             last_token=state.get("last_token"), position_table=self.position_table, scale=self.scale,
+                             copies=self.copies)
 
 
 @HEADS.register("linear")

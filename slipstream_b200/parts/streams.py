@@ -54,13 +54,16 @@ class ConnectedNorm(Norm):
 
     ``tensor``: the norm's weight vector.  ``connection``: prefix of the branch's ``.in``, ``.out`` and ``.mix``
     tensors; None stands for in = 1 (the plain sum) and, for `write_of`, out = 1 and mix = identity, which needs
-    no tensors.  All arithmetic is float32; the result is rounded once."""
+    no tensors.  ``offset``: the stored weight vector lies around zero and the norm multiplies by ``offset + weight``
+    (formed once, in float32).  All arithmetic is float32; the result is rounded once."""
 
     cuda_graph_safe = True
 
-    def __init__(self, tensor: str, size: int, eps: float, streams: int = 1, connection: str | None = None) -> None:
+    def __init__(self, tensor: str, size: int, eps: float, streams: int = 1, connection: str | None = None,
+                 offset: float = 0.0) -> None:
         if not 1 <= streams <= 8:
             raise ValueError("between 1 and 8 residual streams")
+        self.offset = float(offset)
         self.tensor = tensor
         self.size = size
         self.eps = float(eps)
@@ -68,7 +71,8 @@ class ConnectedNorm(Norm):
         self.connection = connection
 
     def weight_specs(self) -> list[WeightSpec]:
-        specs = [WeightSpec(self.tensor, (self.size,), kind="vector", init=("one_plus_normal", 0.1))]
+        specs = [WeightSpec(self.tensor, (self.size,), kind="vector",
+                            init=("normal", 0.1) if self.offset else ("one_plus_normal", 0.1))]
         if self.connection is not None:
             s = self.streams
             specs += [WeightSpec(f"{self.connection}.in", (s,), kind="vector", init=("one_plus_normal", 0.2)),
@@ -79,6 +83,8 @@ class ConnectedNorm(Norm):
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         self.weight = weights[self.tensor]
+        if self.offset:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
         s, dev = self.streams, runtime.device
         if self.connection is not None:
             self.w_in = weights[f"{self.connection}.in"].to(torch.float32).contiguous()
