@@ -52,6 +52,7 @@ class DecoderLM:
         self.position_encoding = position_encoding
         self.order = order if order is not None else [ExecEntry(i) for i in range(len(blocks))]
         self.bindings: list[LayerBinding] = []
+        self.embedding_state: dict[str, torch.Tensor] = {}  # filled by attach_store when the embedding keeps state
         self._plan_cache()
 
     # ------------------------------------------------------------------ structure
