@@ -19,6 +19,10 @@ at three sizes, and every kernel the design adds beside the like kernel of the Q
 attention layers with query/key norms, rotated values and soft-capped scores in turn, routed experts beside a shared
 one, grouped norms on the branches' outputs).
 
+``--compare bezutar`` does the same for the Bezutar decoder (matrix-memory and gated-recurrence layers with per-request
+state, latent attention over one cached row per token with sinks, a convolution over every mixer's input, an embedding
+summed from three tables, hyper-connected streams, a feed-forward without a gate branch).
+
 ``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
 headline): ``--only decode --batch 1 --prompt-len 32000 --context-len 32768`` is a decode step behind a long
 context, ``--only prefill --chunk 512 --prefix 8192 --context-len 32768`` a prompt portion behind cached tokens.
@@ -811,6 +815,249 @@ def run_compare_sarudra(args) -> int:
     return 0
 
 
+def bezutar_config(z: dict, streams: int) -> dict:
+    """config.json of a Bezutar decoder at the layer sizes ``z``: a matrix-memory layer, a latent-attention layer, a
+    gated-recurrence layer and a latent-attention layer that reads the rows of the one before, in turn.  The matrix memory
+    has the attention's heads and head size; latent attention caches 96 + 32 elements a token (rows of 128, the size the
+    tcgen05 attention kernels take); the feed-forward without a gate branch is half again as wide as the gated one, so
+    that a token's feed-forward does the same work."""
+    rot = dict(base=1000000.0, dims=32, scaling=dict(factor=4.0, original=2048, fast=32.0, slow=1.0))
+    layers = []
+    for i in range(z["layers"]):
+        if i % 4 == 0:
+            kind, mixer = "mlstm", dict(heads=z["heads"], dim=z["dim"], vdim=z["dim"], gate_cap=15.0)
+        elif i % 4 == 2:
+            kind, mixer = "mingru", dict(width=z["width"])
+        else:
+            kind = "latent_attention"
+            mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=32, vdim=z["dim"], q_rank=max(z["width"] // 4, 256) // 64 * 64,
+                         kv_rank=96, scale=(z["dim"] + 32) ** -0.5, rot=rot)
+            if i % 4 == 3:
+                mixer["kv_from"] = i - 2
+        layers.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=z["ff"] * 3 // 2)))
+    return dict(architecture="Bezutar", vocab=z["vocab"], width=z["width"], streams=streams, norm=dict(eps=1e-6),
+                canon=dict(taps=4), embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)),
+                max_positions=8192, layers=layers)
+
+
+def run_compare_bezutar(args) -> int:
+    """The Bezutar decoder beside the Qwen2.5 decoder at equal layer sizes (whole steps), then every kernel the design
+    adds, alone at the 7B layer sizes, beside its nearest relative among the kernels of the other decoders."""
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.context import query_tiles_longest_first_host
+
+    pk, pk_kind = peaks()
+    rng = np.random.default_rng(0)
+    dev = torch.device("cuda:0")
+    batch, ctx_tokens, T, page = args.batch, args.prompt_len, args.chunk, 16
+    result: dict = {"compare": "bezutar", "peaks": pk_kind, "batch": batch, "context": ctx_tokens, "prefill_tokens": T,
+                    "streams": args.streams, "sizes": {}}
+    for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
+        qwen, _ = compare_configs(COMPARE_SIZES[name], 8192, 1, False)
+        result["sizes"][name] = {}
+        for which, config in (("qwen2", qwen), ("bezutar", bezutar_config(COMPARE_SIZES[name], args.streams))):
+            if which == "qwen2" and args.skip_qwen2:
+                continue
+            print(f"[bench] {name} {which} ...", file=sys.stderr, flush=True)
+            result["sizes"][name][which] = measure_model(config, args, pk, rng)
+            print(f"[bench] {name} {which}: {result['sizes'][name][which]}", file=sys.stderr, flush=True)
+    if args.no_kernels:
+        print(json.dumps(result))
+        return 0
+
+    print("[bench] single kernels ...", file=sys.stderr, flush=True)
+    z = COMPARE_SIZES["7b"]
+    h, n_q, n_kv, d, inter = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"]
+    lat = bezutar_config(z, args.streams)["layers"][1]["mixer"]
+    q_rank, kv_rank, rot_dim = lat["q_rank"], lat["kv_rank"], lat["rot_dim"]
+    row = kv_rank + rot_dim
+    ff = inter * 3 // 2
+    gen = torch.Generator(device=dev).manual_seed(1)
+    COPIES = 6  # operands of each timed launch rotate through this many copies
+
+    def rand(*shape, dtype=torch.bfloat16, std=0.5):
+        return (torch.randn(*shape, generator=gen, device=dev) * std).to(dtype)
+
+    def sweep(run, copies=COPIES) -> float:
+        for i in range(copies):
+            run(i)
+        times = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(copies):
+                run(i)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / copies)
+        return sorted(times)[2]
+
+    kernels: dict = {}
+
+    def hbm(name: str, us: float, nbytes: float, **more) -> None:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        kernels[name] = {"us": round(us, 2), "gbs": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 3), **more}
+
+    def tensor(name: str, us: float, flops: float) -> None:
+        tf = flops / (us * 1e-6) / 1e12
+        kernels[name] = {"us": round(us, 2), "tflops": round(tf, 1), "bf16_frac": round(tf / pk["bf16_tflops"], 3)}
+
+    def step(q_lens, seq_lens):
+        starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+        as_dev = lambda v: torch.tensor(np.asarray(v), dtype=torch.int32, device=dev)  # noqa: E731
+        positions = np.concatenate([np.arange(s - n, s) for n, s in zip(q_lens, seq_lens)])
+        return types.SimpleNamespace(q_start=as_dev(starts), seq_lens=as_dev(seq_lens), state_slots=as_dev(np.arange(len(q_lens))),
+                                     positions=as_dev(positions), num_requests=len(q_lens),
+                                     is_decode_only=all(n == 1 for n in q_lens))
+
+    table_rows = 65536  # rows of each embedding table here: rows are gathered, the tables' size does not matter
+    tables3 = [rand(table_rows, h) for _ in range(3)]
+    for tokens, tag, ctx in ((T, "prefill", step([T], [T])), (batch, "decode", step([1] * batch, [ctx_tokens] * batch))):
+        R = ctx.num_requests
+        # embedding
+        ids = torch.randint(0, table_rows, (tokens,), generator=gen, device=dev, dtype=torch.int32)
+        last = torch.zeros(R, dtype=torch.int32, device=dev)
+        us = sweep(lambda i: ops.embedding(ids, tables3[0]))
+        hbm(f"{tag}_embedding (qwen2)", us, tokens * h * (2 + 4))
+        us = sweep(lambda i: ops.embed_sum(ids, tables3[0], ctx, pair_table=tables3[1][:65522], pair_hash=(65521, 1000003, 31),
+                                           last_token=last, position_table=tables3[2][:8192], copies=args.streams))
+        hbm(f"{tag}_embed_sum (3 rows into {args.streams} streams)", us, tokens * h * (3 * 2 + 4 * args.streams))
+        # the convolution over a mixer's input, beside the state-space layers' convolution over as many channels
+        xs = [rand(tokens, h) for _ in range(COPIES)]
+        w_taps = rand(h, 4, dtype=torch.float32)
+        conv_state = torch.zeros(R, 3, h, device=dev)
+        us = sweep(lambda i: ops.conv_silu(xs[i], 0, h, w_taps, None, conv_state, ctx))
+        hbm(f"{tag}_conv_silu (sarudra)", us, tokens * h * 4.0 + R * 3 * h * 8.0)
+        us = sweep(lambda i: ops.conv_silu(xs[i], 0, h, w_taps, None, conv_state, ctx, plus_input=True))
+        hbm(f"{tag}_input + convolution", us, tokens * h * 4.0 + R * 3 * h * 8.0)
+        # matrix memory: the cell and its output norm, beside the state-space scan of equal state (heads x 128 x 128)
+        qkvg = [rand(tokens, n_q * 4 * d) for _ in range(COPIES)]
+        gates = [rand(tokens, 2 * n_q, dtype=torch.float32, std=3.0) for _ in range(COPIES)]
+        bias = rand(n_q, dtype=torch.float32)
+        memory = [torch.zeros(R, n_q, d + 1, d, device=dev) for _ in range(COPIES)]
+        peak = torch.zeros(R, n_q, device=dev)
+        us = sweep(lambda i: ops.matrix_cell(qkvg[i], gates[i], bias, bias, 15.0, d ** -0.5, memory[i], peak, ctx, n_q, d, d))
+        state_bytes = R * n_q * (d + 1) * d * 8.0
+        hbm(f"{tag}_matrix_cell", us, state_bytes + tokens * n_q * d * (3 * 2.0 + 4.0),
+            fp32_tflops=round(6.0 * tokens * n_q * (d + 1) * d / us / 1e6, 2))
+        num, nq, peaks_t = ops.matrix_cell(qkvg[0], gates[0], bias, bias, 15.0, d ** -0.5, memory[0], peak, ctx, n_q, d, d)
+        w_cell = rand(n_q * d, dtype=torch.float32)
+        us = sweep(lambda i: ops.cell_output(num, nq, peaks_t, w_cell, qkvg[i][:, 3 * n_q * d:], n_q, d, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_cell_output (head norm, gate)", us, tokens * n_q * d * (4.0 + 2.0 + 2.0))
+        s_heads, s_p, s_n, s_g = n_q, d, d, 4
+        chans = s_heads * s_p + 2 * s_g * s_n
+        xbcs = [rand(tokens, chans) for _ in range(COPIES)]
+        dts = [rand(tokens, s_heads) for _ in range(COPIES)]
+        dt_bias, a_log, d_skip = (rand(s_heads, dtype=torch.float32) for _ in range(3))
+        states = [torch.zeros(R, s_heads, s_p, s_n, device=dev) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.ssm_scan(xbcs[i], dts[i], dt_bias, a_log, d_skip, states[i], ctx, s_heads, s_g, s_p, s_n))
+        hbm(f"{tag}_ssm_scan of equal state (sarudra)", us, R * s_heads * s_p * s_n * 8.0 + tokens * (chans * 2.0 + s_heads * s_p * 4.0),
+            fp32_tflops=round(6.0 * tokens * s_heads * s_p * s_n / us / 1e6, 2))
+        del qkvg, gates, memory, xbcs, dts, states, num
+        # gated recurrence
+        projs = [rand(tokens, 3 * h) for _ in range(COPIES)]
+        cell = torch.zeros(R, h, device=dev)
+        bias2 = rand(2 * h, dtype=torch.float32)
+        us = sweep(lambda i: ops.gated_recurrence(projs[i], h, cell, ctx, bias=bias2))
+        hbm(f"{tag}_gated_recurrence", us, tokens * h * (3 * 2.0 + 2.0) + R * h * 8.0)
+        del projs
+        # feed-forward activation
+        ups = [rand(tokens, ff) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.xielu(ups[i], 0.7, 1.2))
+        hbm(f"{tag}_xielu (in place)", us, tokens * ff * 4.0)
+        gus = [rand(tokens, 2 * inter) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.swiglu(gus[i], block=64))
+        hbm(f"{tag}_swiglu by itself (qwen2)", us, tokens * inter * 6.0)
+        del ups, gus
+        # latent attention: latents, rotation and page write; the products per head
+        positions = ctx.positions
+        slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+        downs = [rand(tokens, (q_rank + row + n_q + 7) // 8 * 8) for _ in range(COPIES)]
+        kvs = [torch.zeros((tokens + page - 1) // page + 1, 2, 1, page, row, dtype=torch.bfloat16, device=dev) for _ in range(COPIES)]
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))).to(dev)
+        qw, kw = rand(q_rank, dtype=torch.float32), rand(kv_rank, dtype=torch.float32)
+        us = sweep(lambda i: ops.latent_rows(downs[i], positions, slots, kvs[i], qw, kw, inv_freq, 1.1, q_rank, kv_rank, rot_dim, 1e-6))
+        hbm(f"{tag}_latent_rows (two norms, rotation, page write)", us, tokens * 2.0 * (2 * q_rank + row + 2 * row))
+        width = (n_q + 2 * n_kv) * d
+        rows = [rand(tokens, width) for _ in range(COPIES)]
+        kvq = [torch.zeros((tokens + page - 1) // page + 1, 2, n_kv, page, d, dtype=torch.bfloat16, device=dev) for _ in range(COPIES)]
+        inv_d = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        us = sweep(lambda i: ops.rope_and_cache(rows[i], positions, slots, inv_d, kvq[i], n_q, n_kv, d, d))
+        hbm(f"{tag}_rope_and_cache (qwen2)", us, tokens * d * 2.0 * (2 * n_q + 4 * n_kv))
+        del rows, kvq, kvs
+        qs = [rand(tokens, n_q * (d + rot_dim)) for _ in range(COPIES)]
+        to_latent, to_value = rand(n_q, d, kv_rank, std=0.1), rand(n_q, kv_rank, d, std=0.1)
+        q_lat = torch.empty(tokens, n_q * row, dtype=torch.bfloat16, device=dev)
+        us = sweep(lambda i: ops.head_product(qs[i], d + rot_dim, to_latent, q_lat, row, turn=rot_dim, pad_to=row, positions=positions,
+                                              inv_freq=inv_freq, mscale=1.1))
+        flops = 2.0 * tokens * n_q * d * kv_rank
+        moved = tokens * n_q * (d + rot_dim + row) * 2.0 + n_q * d * kv_rank * 2.0
+        kernels[f"{tag}_head_product into the latent space (+ rotation)"] = {
+            "us": round(us, 2), "tflops": round(flops / us / 1e6, 2), "gbs": round(moved / us / 1e3, 1),
+            "hbm_frac": round(moved / us / 1e3 / pk["hbm_gbs"], 3)}
+        vals = torch.empty(tokens, n_q * d, dtype=torch.bfloat16, device=dev)
+        mixed = [rand(tokens, n_q * row) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.head_product(mixed[i], row, to_value, vals, d, gates=downs[i][:, q_rank + row: q_rank + row + n_q]))
+        moved = tokens * n_q * (row + d) * 2.0 + n_q * d * kv_rank * 2.0
+        kernels[f"{tag}_head_product up to values (+ gate)"] = {
+            "us": round(us, 2), "tflops": round(flops / us / 1e6, 2), "gbs": round(moved / us / 1e3, 1),
+            "hbm_frac": round(moved / us / 1e3 / pk["hbm_gbs"], 3)}
+        del qs, mixed, downs
+
+    # attention: every design's own kernel over the same number of cached tokens
+    def tables(n_req: int, tokens: int) -> torch.Tensor:
+        per = (tokens + page - 1) // page
+        return torch.arange(n_req * per, dtype=torch.int32, device=dev).view(n_req, per)
+
+    n_pages = batch * ((max(ctx_tokens, T) + page - 1) // page) + 1
+    sinks = rand(n_q, dtype=torch.float32)
+    q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    lens = torch.full((batch,), ctx_tokens, dtype=torch.int32, device=dev)
+    table = tables(batch, ctx_tokens)
+    stages = ops.functions.DECODE_RING_STAGES
+    kv_pages = [rand(n_pages, 2, n_kv, page, d) for _ in range(COPIES)]
+    qkv = rand(batch, (n_q + 2 * n_kv) * d)
+    att = torch.empty(batch, n_q * d, dtype=torch.bfloat16, device=dev)
+    slices = ops.decode_slices(batch, n_kv, n_q // n_kv, ctx_tokens, False, ops.sm_count(dev))
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv_pages[i], table, q_start, lens, batch, n_q,
+                                                    n_kv, d, d ** -0.5, 0, slices, stages=stages))
+    hbm(f"decode_attention (qwen2: {n_q} heads on {n_kv} cached heads of {d})", us, batch * ctx_tokens * 2.0 * n_kv * d * 2 + 2.0 * batch * n_q * d * 2)
+    qkv_p = rand(T, (n_q + 2 * n_kv) * d)
+    att_p = torch.empty(T, n_q * d, dtype=torch.bfloat16, device=dev)
+    table_p, q_start_p = tables(1, T), torch.tensor([0, T], dtype=torch.int32, device=dev)
+    lens_p = torch.tensor([T], dtype=torch.int32, device=dev)
+    req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(
+        np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), 128 // (n_q // n_kv)))
+    us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req, tok0,
+                                                             q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1))
+    tensor("prefill_attention tcgen05 (qwen2)", us, 4.0 * n_q * d * (T * (T + 1) // 2))
+    del kv_pages
+    lat_pages = [rand(n_pages, 2, 1, page, row) for _ in range(COPIES)]
+    q_lat = rand(batch, n_q * row)
+    att_l = torch.empty(batch, n_q * row, dtype=torch.bfloat16, device=dev)
+    slices = ops.decode_slices(batch, 1, n_q, ctx_tokens, False, ops.sm_count(dev))
+    us = sweep(lambda i: ops.paged_attention_decode(q_lat, q_lat.shape[1], att_l, lat_pages[i], table, q_start, lens, batch, n_q,
+                                                    1, row, 0.08, 0, slices, stages=stages, sinks=sinks))
+    hbm(f"decode_attention with sinks ({n_q} heads on one cached row of {row})", us, batch * ctx_tokens * 2.0 * row * 2 + 2.0 * batch * n_q * row * 2)
+    q_lat_p = rand(T, n_q * row)
+    att_lp = torch.empty(T, n_q * row, dtype=torch.bfloat16, device=dev)
+    if ops.tcgen05_prefill_fits(row, n_q, 1, page):
+        req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(
+            np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), 128 // n_q))
+        parts = ops.prefill_key_parts(np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), 128 // n_q, 1)
+        us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(q_lat_p, q_lat_p.shape[1], att_lp, lat_pages[i], table_p, req, tok0,
+                                                                 q_start_p, lens_p, n_q, 1, row, 0.08, parts, sinks=sinks))
+        tensor(f"prefill_attention tcgen05 with sinks ({n_q} heads on one cached row of {row})", us, 4.0 * n_q * row * (T * (T + 1) // 2))
+    ops.check_errors(dev)
+    result["kernels_7b"] = kernels
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -830,7 +1077,7 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
     ap.add_argument("--window", type=int, default=4096, help="--compare sarudra: positions of the sliding window")
-    ap.add_argument("--compare", choices=["fokedra", "sarudra"], default=None,
+    ap.add_argument("--compare", choices=["fokedra", "sarudra", "bezutar"], default=None,
                     help="time another decoder design beside the Qwen2.5 decoder at equal layer sizes instead")
     ap.add_argument("--sizes", default="", help="--compare: which of 0.5b,7b,14b (default: all)")
     ap.add_argument("--mask-chunk", type=int, default=8192, help="--compare: positions per attention chunk")
@@ -850,6 +1097,8 @@ def main() -> int:
         if args.steps == 256:
             args.steps = 64
         args.warmup = max(args.warmup, 3)
+        if args.compare == "bezutar":
+            return run_compare_bezutar(args)
         return run_compare_sarudra(args) if args.compare == "sarudra" else run_compare(args)
     if args.workload:
         return run_workload(args.workload, args)

@@ -99,7 +99,7 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
                                    const int32_t* tile_req, const int32_t* tile_tok0, int n_tiles,
                                    const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv, int page_size,
                                    int64_t num_pages, float scale, int splits, int span, int* err, cudaStream_t stream,
-                                   float softcap) {
+                                   float softcap, const float* sinks) {
     if (n_tiles <= 0) return 0;
     const int G = n_q / n_kv;
     if (G < 1 || G > 128 || page_size % 8 != 0 || 64 % page_size != 0 || q_stride % 8 != 0) return -3003;
@@ -116,7 +116,7 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
     a.out = (bf16*)out; a.out_stride = out_stride; a.block_tables = block_tables; a.max_blocks = max_blocks;
     a.tile_req = tile_req; a.tile_tok0 = tile_tok0; a.q_start = q_start; a.seq_lens = seq_lens;
     a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.err = err;
-    a.span = span; a.softcap = softcap;
+    a.span = span; a.softcap = softcap; a.sinks = sinks;
     constexpr int smem = fa::smem_bytes<HEAD_DIM>();
     static SsPerDevice opted;
     if (int rc_smem = ss_opt_in_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem, opted)) return rc_smem;

@@ -151,6 +151,7 @@ struct Args {
     int* err;
     int span;  // what a query sees besides the causal rule (common.cuh: key_floor); 0: every earlier key
     float softcap;  // > 0: a scaled score s enters the softmax as softcap * tanh(s / softcap)
+    const float* sinks;  // float32 [n_q] or null: one more term exp(sinks[h]) in the denominator of head h's softmax
 };
 
 template <int D>
@@ -470,6 +471,9 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (splits == 1) {
             if (ok) {
+                // a sink has no key and no value and counts once: its term joins the sum, in the sum's own units
+                if (a.sinks && valid)
+                    l = m_ref == -INFINITY ? 1.f : l + ex2(a.sinks[kvh * G + g] * 1.4426950408889634f - m_ref);
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D;
 #pragma unroll 1
@@ -533,10 +537,12 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 w[sp] = (sp < splits && ms[sp] != -INFINITY) ? ex2(ms[sp] - m_all) : 0.f;
                 if (sp < splits) l_all += w[sp] * ld_cluster_f32(Lsm + row, (uint32_t)sp);
             }
-            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
             const int cols = D / splits, c0 = part * cols;  // D / splits is a multiple of 8: 8 bfloat16 per store
             const bool valid = row < rows_valid;
             const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
+            if (a.sinks && valid)  // once for the row, whichever block of the cluster writes these columns
+                l_all = m_all == -INFINITY ? 1.f : l_all + ex2(a.sinks[kvh * G + g] * 1.4426950408889634f - m_all);
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
             bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D + c0;
 #pragma unroll 1
             for (int c = 0; c < cols; c += 8) {

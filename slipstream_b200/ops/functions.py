@@ -104,7 +104,7 @@ _ATTN_SIGNATURES = {
                             c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                            c_void_p, c_void_p, c_float],
+                            c_void_p, c_void_p, c_float, c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float],
@@ -627,7 +627,7 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                     block_tables: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
                                     q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
                                     head_dim: int, scale: float, key_parts: int = 1, chunk: int = 0, window: int = 0,
-                                    softcap: float = 0.0) -> None:
+                                    softcap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
     """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
     tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
     one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows); blocks
@@ -635,8 +635,10 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
     ``key_parts`` (1, 2, 4 or 8): the keys of every query tile are shared by that many blocks, a thread-block
     cluster whose results are combined through shared memory (see ``prefill_key_parts``).  ``chunk`` C: a query sees
     only the earlier keys of its own chunk of C positions; the key tiles in front of a query tile's first chunk are
-    never fetched."""
+    never fetched.  ``sinks`` (float32 [n_q]): one more term ``exp(sinks[h])`` in the denominator of head h, added where
+    a row's sum is complete (by the block that writes the row, or once where a cluster combines its parts)."""
     _need(out, torch.bfloat16, "attention output")
+    _check_sinks(sinks, n_q)
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention kernels take bfloat16")
@@ -651,7 +653,7 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                    tile_tok0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(key_parts),
                                    key_span(window, chunk), error_word(q.device).data_ptr(), _stream(),
-                                   float(softcap or 0.0)),
+                                   float(softcap or 0.0), _ptr(sinks)),
            "paged_attention_prefill_tcgen05")
 
 
@@ -834,8 +836,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     ``gate``: a view of ``qkv`` [N, n_q * D]; the output is multiplied by its sigmoid, inside the attention kernel
     except behind the tcgen05 prefill kernel, where `sigmoid_gate` follows.
 
-    ``sinks`` (float32 [n_q]): one more term ``exp(sinks[h])`` in the softmax's denominator of head h; such layers run the
-    CUDA-core kernel or the mma.sync kernels."""
+    ``sinks`` (float32 [n_q]): one more term ``exp(sinks[h])`` in the softmax's denominator of head h; decode steps of
+    such layers run the cp.async kernel."""
     if rope is not None and not (qkv.dtype == torch.bfloat16 and ctx.is_decode_only):
         raise KernelError("only bfloat16 decode steps rotate inside the attention kernel")
     if qkv.dtype == torch.float32:
@@ -856,7 +858,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
                                stages=DECODE_RING_STAGES, chunk=chunk, gate=gate, softcap=softcap, sinks=sinks)
         return
-    if sinks is None and tcgen05_prefill_fits(head_dim, n_q, n_kv, kv.shape[3]):
+    if tcgen05_prefill_fits(head_dim, n_q, n_kv, kv.shape[3]):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv, window or chunk)
         parts = ctx.extras.get(key)
@@ -864,7 +866,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
             parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv,
                                                         sm_count(qkv.device), window or chunk)
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
-                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts, chunk, window, softcap)
+                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts, chunk, window, softcap, sinks)
         if gate is not None:
             sigmoid_gate(out, gate)
         return

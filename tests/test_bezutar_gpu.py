@@ -758,15 +758,15 @@ def test_a_sink_left_out_a_lost_state_or_a_wrong_pair_row_would_show(models, tmp
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_portions_at_sizes_the_tensor_core_paths_take(tmp_path, dtype):
-    """A wider model whose sizes are in steps of 64: in bfloat16 a portion of 600 tokens takes the tcgen05 products and
-    the tcgen05 prefill attention over cached rows of 192 elements with 8 query heads on the one cached row; then
-    portions beside decoded tokens."""
+    """A wider model whose sizes are in steps of 64: in bfloat16 a portion of 600 tokens takes the tcgen05 products and,
+    cached rows being 128 elements, the tcgen05 prefill attention with 8 (and, for the layer that borrows the rows, 4)
+    query heads on the one cached row and their sinks; then portions beside decoded tokens."""
     config = {"architecture": "Bezutar", "vocab": 300, "width": 256, "streams": 2, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
               "embedding": {"bigram": {"buckets": 257, "mul_prev": 13, "mul_cur": 5}}, "max_positions": 1024,
               "layers": [layer(mlstm(4, 64, 128, 15.0), dense(512)),
-                         layer(latent(8, 64, 64, 64, 192, 128, 0.09, 10000.0, (4.0, 256, 32.0, 1.0)), dense(256)),
+                         layer(latent(8, 64, 64, 64, 192, 64, 0.09, 10000.0, (4.0, 256, 32.0, 1.0)), dense(256)),
                          layer(mingru(384), dense(256)),
-                         layer(latent(4, 128, 64, 128, 128, 128, 0.07, 10000.0, (4.0, 256, 32.0, 1.0), kv_from=1), None)]}
+                         layer(latent(4, 128, 64, 128, 128, 64, 0.07, 10000.0, (4.0, 256, 32.0, 1.0), kv_from=1), None)]}
     if dtype == "bfloat16":
         config = cooled(config)
     weights = write_model(tmp_path, config, 77, heat=1.0 if dtype == "float32" else 0.3)

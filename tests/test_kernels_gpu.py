@@ -175,7 +175,7 @@ def make_attention_case(dtype, lens, q_lens, n_q, n_kv, d, page, seed, sharp=Non
             torch.tensor(lens, dtype=torch.int32, device=DEV))
 
 
-def attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window):
+def attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window, sinks=None):
     N, n_q, d = q.shape
     out = torch.zeros(N, n_q, d, dtype=torch.float64)
     qd, kvd = q.double().cpu(), kv.double().cpu()
@@ -195,7 +195,11 @@ def attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, wind
             if window:
                 ok &= key > pos - window
             s = s.masked_fill(~ok, float("-inf"))
-            out[a:b, h] = torch.softmax(s, -1) @ V[h // G]
+            if sinks is not None:  # one more column in the softmax, without a value
+                s = torch.cat([s, sinks[h].double().cpu().expand(T, 1)], dim=-1)
+                out[a:b, h] = torch.softmax(s, -1)[:, :-1] @ V[h // G]
+            else:
+                out[a:b, h] = torch.softmax(s, -1) @ V[h // G]
     return out
 
 
@@ -602,6 +606,29 @@ def test_tcgen05_prefill_attention(case):
         out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
         ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens,
                                               n_q, n_kv, d, scale, parts)
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, parts
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("case", [0, 1, 3, 4])
+def test_tcgen05_prefill_attention_with_sinks(case):
+    """One more term per head in every row's denominator: small ones, ones that outweigh every key, and ones far below;
+    added once, whether a block has a row's keys to itself or a cluster shares them."""
+    lens, q_lens, n_q, n_kv, d, page = TC5_CASES[case]
+    q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, q_lens, n_q, n_kv, d, page, seed=90 + case)
+    scale = d ** -0.5
+    sinks = torch.linspace(-3.0, 6.0, n_q, device=DEV)
+    sinks[0], sinks[-1] = -80.0, 40.0
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0, sinks=sinks)
+    plain = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0)
+    assert rel_err(plain[:, 1:-1], ref[:, 1:-1]) > 0.2 and rel_err(plain[:, 0], ref[:, 0]) < 1e-9 and ref[:, -1].abs().max() < 1e-9
+    from slipstream_b200.engine.context import query_tiles_host
+    tok = 128 // (n_q // n_kv)
+    req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(np.asarray(q_lens, dtype=np.int32), tok))
+    for parts in (1, 2, 8):
+        out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens,
+                                              n_q, n_kv, d, scale, parts, sinks=sinks)
         assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, parts
     ops().check_errors(torch.device(DEV))
 
