@@ -120,34 +120,74 @@ extern "C" int ss_embed_sum(const int32_t* tokens, const int32_t* positions, con
 // The kernel treats n as one more column of S (the column of a value that is always 1) and writes, per token,
 // the numerators S_t^T q_t [V], the scalar n_t . q_t and m_t; the norm kernel behind it divides.
 // State: memory [slot][H][V + 1][D] float32 (column-major, column V is n), peak [slot][H] (m, starts at 0).
-// A block: one request, one head, MC_COLS columns; a column is shared by MC_LANES lanes, lane j holding rows
-// d = i * MC_LANES + j.  Tokens are staged MC_TOKENS at a time in shared memory as float32.
+//
+// A block: one request, one head, MC_WARPS * 4 * CPT columns.  A compute warp holds four groups of CPT columns; a group
+// is shared by MC_LANES lanes, lane j holding rows d = i * 4 MC_LANES + 4 j + (0 .. 3), i < NI, of each of its columns
+// in registers (a lane reads q and k as 16-byte words that neighbouring lanes continue).  Three more warps stage the
+// next MC_TOKENS tokens as float32 in the other half of shared memory (one q, scaled; one k; one the block's values
+// and the gates with their chain m) while the compute warps walk the staged ones; rows past the last token
+// are staged as k = q = 0 with keep = 1 and take = 0, so that a group of MC_GROUP tokens is always walked whole.  The
+// dot products of a group of tokens are reduced together: a lane hands half of its columns' partial sums to its
+// partner at each step.
 #define MC_LANES 8
-#define MC_COLS 16
-#define MC_TOKENS 16
-#define MC_THREADS (MC_LANES * MC_COLS)
+#define MC_TOKENS 32  // a lane of the staging warp a token
+#define MC_GROUP 4
+#define MC_WARPS 2
+#define MC_THREADS ((MC_WARPS + 3) * 32)
+static_assert(MC_TOKENS == 32 && MC_TOKENS % MC_GROUP == 0, "the gates of a batch are one warp wide");
 
-template <typename T, int DPL>
+// 16 bytes of T as floats
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&v)[8], bf16) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        v[2 * e] = __uint_as_float(w[e] << 16);
+        v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&v)[4], float) {
+    v[0] = __uint_as_float(raw.x); v[1] = __uint_as_float(raw.y); v[2] = __uint_as_float(raw.z); v[3] = __uint_as_float(raw.w);
+}
+
+// The sum over a group's 8 lanes of CPT values each; lane j ends with the sum of column `column_of_lane<CPT>(j)`.
+template <int CPT> __device__ __forceinline__ int column_of_lane(int j) {
+    return CPT == 4 ? ((j >> 2) & 1) * 2 + ((j >> 1) & 1) : (j >> 2) & 1;
+}
+template <int CPT> __device__ __forceinline__ float sum_columns(const float (&a)[CPT], int j) {
+    float x;
+    const bool up = j & 4;
+    if constexpr (CPT == 4) {
+        float x0 = up ? a[2] : a[0], x1 = up ? a[3] : a[1];
+        x0 += __shfl_xor_sync(0xffffffffu, up ? a[0] : a[2], 4);
+        x1 += __shfl_xor_sync(0xffffffffu, up ? a[1] : a[3], 4);
+        const bool mid = j & 2;
+        x = mid ? x1 : x0;
+        x += __shfl_xor_sync(0xffffffffu, mid ? x0 : x1, 2);
+    } else {
+        static_assert(CPT == 2, "two or four columns a lane");
+        x = up ? a[1] : a[0];
+        x += __shfl_xor_sync(0xffffffffu, up ? a[0] : a[1], 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+    }
+    return x + __shfl_xor_sync(0xffffffffu, x, 1);
+}
+
+template <typename T, int NI, int CPT>
 __global__ void __launch_bounds__(MC_THREADS)
 matrix_cell_kernel(const T* __restrict__ qkv, int64_t stride, const float* __restrict__ gates, int64_t gate_stride,
                    const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, float q_scale,
                    float* __restrict__ memory, float* __restrict__ peak, float* __restrict__ num, float* __restrict__ nq,
                    float* __restrict__ peaks_out, const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
-                   const int32_t* __restrict__ slots, int H, int D, int V, int n_slots, int* err) {
+                   const int32_t* __restrict__ slots, int H, int D, int V, int n_slots, int wide_loads, int* err) {
     pdl_wait();
-    extern __shared__ float cell_smem[];
-    float* qs = cell_smem;                       // [MC_TOKENS][D]
-    float* ks = qs + MC_TOKENS * D;              // [MC_TOKENS][D]
-    float* vs = ks + MC_TOKENS * D;              // [MC_TOKENS][MC_COLS]
-    float* gi = vs + MC_TOKENS * MC_COLS;        // [MC_TOKENS] each: i, f, keep, take, m
-    float* gf = gi + MC_TOKENS;
-    float* keep_s = gf + MC_TOKENS;
-    float* take_s = keep_s + MC_TOKENS;
-    float* m_s = take_s + MC_TOKENS;
+    constexpr int DP = NI * 4 * MC_LANES;            // rows as staged: zeros from D on
+    constexpr int COLS = MC_WARPS * 4 * CPT;         // columns of a block
+    constexpr int HALF = 2 * MC_TOKENS * DP + MC_TOKENS * COLS + 5 * MC_TOKENS;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    extern __shared__ __align__(16) float cell_smem[];
 
-    const int tid = threadIdx.x, j = tid & (MC_LANES - 1), col_here = tid / MC_LANES;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, r = blockIdx.z;
-    const int col = blockIdx.x * MC_COLS + col_here;  // V: the column of n
     const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
     if (q_len <= 0 || seq_lens[r] <= 0) return;
     const int slot = slots[r];
@@ -155,83 +195,223 @@ matrix_cell_kernel(const T* __restrict__ qkv, int64_t stride, const float* __res
         if (tid == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         return;
     }
-    const bool col_ok = col <= V;
-    float* mem = memory + (((int64_t)slot * H + h) * (V + 1) + (col_ok ? col : 0)) * D;
-    float S[DPL];
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int d = i * MC_LANES + j;
-        S[i] = (col_ok && d < D) ? mem[d] : 0.f;
-    }
-    float m_prev = peak[(int64_t)slot * H + h];
-    const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+    const int n_batches = (q_len + MC_TOKENS - 1) / MC_TOKENS;
+    const bool stager = warp >= MC_WARPS, stages_gates = warp == MC_WARPS + 2;
 
-    for (int t0 = 0; t0 < q_len; t0 += MC_TOKENS) {
-        const int n = min(MC_TOKENS, q_len - t0);
-        __syncthreads();  // the batch before has been used
-        for (int idx = tid; idx < n * D; idx += MC_THREADS) {
-            const int t = idx / D, d = idx - t * D;
-            const T* src = qkv + (int64_t)(q0 + t0 + t) * stride + (int64_t)h * D + d;
-            qs[t * D + d] = to_float(src[0]) * q_scale;
-            ks[t * D + d] = to_float(src[(int64_t)H * D]);
-        }
-        for (int idx = tid; idx < n * MC_COLS; idx += MC_THREADS) {
-            const int t = idx / MC_COLS, c = idx - t * MC_COLS, gc = blockIdx.x * MC_COLS + c;
-            vs[idx] = gc < V ? to_float(qkv[(int64_t)(q0 + t0 + t) * stride + 2 * (int64_t)H * D + (int64_t)h * V + gc])
-                             : (gc == V ? 1.f : 0.f);
-        }
-        if (tid < n) {
-            const float* g = gates + (int64_t)(q0 + t0 + tid) * gate_stride;
-            gi[tid] = cap * tanhf((g[h] + bi) / cap);
-            gf[tid] = log_sigmoid(cap * tanhf((g[H + h] + bf) / cap));
-        }
-        __syncthreads();
-        if (tid == 0) {  // the running maximum is a chain; everything else of the gates is not
-            float m = m_prev;
-            for (int t = 0; t < n; ++t) {
-                const float carried = gf[t] + m;
-                const float m_new = fmaxf(carried, gi[t]);
-                keep_s[t] = expf(carried - m_new);
-                take_s[t] = expf(gi[t] - m_new);
-                m_s[t] = m_new;
-                m = m_new;
-            }
-        }
-        __syncthreads();
-        m_prev = m_s[n - 1];
-        if (blockIdx.x == 0 && tid < n) peaks_out[(int64_t)(q0 + t0 + tid) * H + h] = m_s[tid];
-        for (int t = 0; t < n; ++t) {
-            const float keep = keep_s[t];
-            const float tv = take_s[t] * vs[t * MC_COLS + col_here];
-            const float* kt = ks + t * D;
-            const float* qt = qs + t * D;
-            float acc = 0.f;
+    // ---- the staging warps: one for q, one for k, one for the values and the gates
+    float m_prev = stages_gates ? peak[(int64_t)slot * H + h] : 0.f;
+    const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+    auto stage = [&](int batch) {
+        float* half = cell_smem + (batch & 1) * HALF;
+        float* vs = half + 2 * MC_TOKENS * DP;     // [MC_TOKENS][COLS], behind q and k [MC_TOKENS][DP] each
+        float* gi = vs + MC_TOKENS * COLS;         // [MC_TOKENS] each: i, f, keep, take, m
+        float* gf = gi + MC_TOKENS;
+        float* keep_s = gf + MC_TOKENS;
+        float* take_s = keep_s + MC_TOKENS;
+        float* m_s = take_s + MC_TOKENS;
+        const int t0 = batch * MC_TOKENS, n = min(MC_TOKENS, q_len - t0);
+        const T* base = qkv + (int64_t)(q0 + t0) * stride;
+        if (!stages_gates) {
+            const bool is_k = warp == MC_WARPS + 1;
+            float* dst = half + (is_k ? MC_TOKENS * DP : 0);
+            const T* rows = base + (is_k ? (int64_t)H * D : 0) + (int64_t)h * D;
+            const float factor = is_k ? 1.f : q_scale;
+            if (wide_loads) {
+                constexpr int PER_ROW = DP / VEC;
+#pragma unroll 8
+                for (int idx = lane; idx < MC_TOKENS * PER_ROW; idx += 32) {
+                    const int t = idx / PER_ROW, d = (idx - t * PER_ROW) * VEC;
+                    float v[VEC];
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                const int d = i * MC_LANES + j;
-                if (d < D) {
-                    S[i] = fmaf(keep, S[i], kt[d] * tv);
-                    acc = fmaf(S[i], qt[d], acc);
+                    for (int e = 0; e < VEC; ++e) v[e] = 0.f;
+                    if (t < n && d < D)  // D is a multiple of VEC here
+                        unpack16(*reinterpret_cast<const uint4*>(rows + (int64_t)t * stride + d), v, T());
+#pragma unroll
+                    for (int e = 0; e < VEC; e += 4)
+                        *reinterpret_cast<float4*>(dst + t * DP + d + e) =
+                            make_float4(v[e] * factor, v[e + 1] * factor, v[e + 2] * factor, v[e + 3] * factor);
+                }
+            } else {
+#pragma unroll 8
+                for (int idx = lane; idx < MC_TOKENS * DP; idx += 32) {
+                    const int t = idx / DP, d = idx - t * DP;
+                    dst[idx] = (t < n && d < D) ? to_float(rows[(int64_t)t * stride + d]) * factor : 0.f;
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (j == 0 && col_ok) {
-                const int64_t row = q0 + t0 + t;
-                if (col < V) num[row * H * V + (int64_t)h * V + col] = acc;
-                else nq[row * H + h] = acc;
+            return;
+        }
+        float a = 0.f, b = 0.f;  // a lane a token
+        if (lane < n) {
+            const float* g = gates + (int64_t)(q0 + t0 + lane) * gate_stride;
+            a = cap * tanhf((g[h] + bi) / cap);
+            b = log_sigmoid(cap * tanhf((g[H + h] + bf) / cap));
+        }
+        gi[lane] = a;
+        gf[lane] = b;
+        const T* vals = base + 2 * (int64_t)H * D + (int64_t)h * V;
+        const int c0 = blockIdx.x * COLS;
+        if (wide_loads) {
+            constexpr int PER_ROW = COLS / VEC;
+#pragma unroll
+            for (int idx = lane; idx < MC_TOKENS * PER_ROW; idx += 32) {
+                const int t = idx / PER_ROW, c = (idx - t * PER_ROW) * VEC;
+                float v[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v[e] = 0.f;
+                if (t < n && c0 + c < V)  // V is a multiple of VEC here
+                    unpack16(*reinterpret_cast<const uint4*>(vals + (int64_t)t * stride + c0 + c), v, T());
+                if (c0 + c == V) v[0] = 1.f;
+#pragma unroll
+                for (int e = 0; e < VEC; e += 4)
+                    *reinterpret_cast<float4*>(vs + t * COLS + c + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            }
+        } else {
+#pragma unroll 8
+            for (int idx = lane; idx < MC_TOKENS * COLS; idx += 32) {
+                const int t = idx / COLS, gc = c0 + idx - t * COLS;
+                float v = gc == V ? 1.f : 0.f;
+                if (t < n && gc < V) v = to_float(vals[(int64_t)t * stride + gc]);
+                vs[idx] = v;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {  // the running maximum is a chain; everything else of the gates is not
+            float m = m_prev;
+            for (int t = 0; t < n; ++t) {
+                m = fmaxf(gf[t] + m, gi[t]);
+                m_s[t] = m;
+            }
+        }
+        __syncwarp();
+        float keep = 1.f, take = 0.f;
+        if (lane < n) {
+            const float before = lane ? m_s[lane - 1] : m_prev, now = m_s[lane];
+            keep = expf(b + before - now);
+            take = expf(a - now);
+            if (blockIdx.x == 0) peaks_out[(int64_t)(q0 + t0 + lane) * H + h] = now;
+        }
+        keep_s[lane] = keep;
+        take_s[lane] = take;
+        m_prev = m_s[n - 1];
+    };
+
+    // ---- the compute warps
+    const int j = lane & (MC_LANES - 1), group = warp * 4 + (lane >> 3);
+    const int col0 = blockIdx.x * COLS + group * CPT;  // this lane's columns: col0 .. col0 + CPT - 1; V is the column of n
+    float S[CPT][NI * 4];
+    const bool rows_of_4 = (D & 3) == 0;
+    if (!stager) {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const bool col_ok = col0 + c <= V;
+            const float* mem = memory + (((int64_t)slot * H + h) * (V + 1) + (col_ok ? col0 + c : 0)) * D;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int d = i * 4 * MC_LANES + 4 * j;
+                if (col_ok && rows_of_4 && d < D) {
+                    const float4 w = *reinterpret_cast<const float4*>(mem + d);
+                    S[c][4 * i] = w.x; S[c][4 * i + 1] = w.y; S[c][4 * i + 2] = w.z; S[c][4 * i + 3] = w.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) S[c][4 * i + e] = (col_ok && d + e < D) ? mem[d + e] : 0.f;
+                }
             }
         }
     }
-    if (col_ok) {
+
+    if (stager) stage(0);
+    __syncthreads();
+    for (int batch = 0; batch < n_batches; ++batch) {
+        if (stager) {
+            if (batch + 1 < n_batches) stage(batch + 1);
+        } else {
+            const float* half = cell_smem + (batch & 1) * HALF;
+            const float4* qs4 = reinterpret_cast<const float4*>(half);
+            const float4* ks4 = reinterpret_cast<const float4*>(half + MC_TOKENS * DP);
+            const float* vs = half + 2 * MC_TOKENS * DP;
+            const float* keep_s = vs + MC_TOKENS * COLS + 2 * MC_TOKENS;
+            const float* take_s = keep_s + MC_TOKENS;
+            const int t0 = batch * MC_TOKENS, n = min(MC_TOKENS, q_len - t0);
+            for (int tg = 0; tg < n; tg += MC_GROUP) {
+                float acc[MC_GROUP][CPT];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            const int d = i * MC_LANES + j;
-            if (d < D) mem[d] = S[i];
+                for (int g = 0; g < MC_GROUP; ++g) {
+                    const int t = tg + g;
+                    const float keep = keep_s[t], take = take_s[t];
+                    float tv[CPT];
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        tv[c] = take * vs[t * COLS + group * CPT + c];
+                        acc[g][c] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < NI; ++i) {
+                        const float4 k4 = ks4[t * (DP / 4) + i * MC_LANES + j], q4 = qs4[t * (DP / 4) + i * MC_LANES + j];
+                        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                        for (int c = 0; c < CPT; ++c) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                S[c][4 * i + e] = fmaf(keep, S[c][4 * i + e], kk[e] * tv[c]);
+                                acc[g][c] = fmaf(S[c][4 * i + e], qq[e], acc[g][c]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < MC_GROUP; ++g) {
+                    const float total = sum_columns<CPT>(acc[g], j);
+                    const int col = col0 + column_of_lane<CPT>(j);
+                    const bool writer = CPT == 4 ? (j & 1) == 0 : (j & 3) == 0;
+                    if (writer && tg + g < n && col <= V) {
+                        const int64_t row = q0 + t0 + tg + g;
+                        if (col < V) num[row * H * V + (int64_t)h * V + col] = total;
+                        else nq[row * H + h] = total;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (stager) {
+        if (stages_gates && blockIdx.x == 0 && lane == 0) peak[(int64_t)slot * H + h] = m_prev;
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        if (col0 + c > V) continue;
+        float* mem = memory + (((int64_t)slot * H + h) * (V + 1) + col0 + c) * D;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int d = i * 4 * MC_LANES + 4 * j;
+            if (rows_of_4 && d < D) {
+                *reinterpret_cast<float4*>(mem + d) = make_float4(S[c][4 * i], S[c][4 * i + 1], S[c][4 * i + 2], S[c][4 * i + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (d + e < D) mem[d + e] = S[c][4 * i + e];
+            }
         }
     }
-    if (blockIdx.x == 0 && tid == 0) peak[(int64_t)slot * H + h] = m_prev;
+}
+
+template <typename T, int NI, int CPT>
+static int launch_matrix_cell_as(const void* qkv, int64_t stride, const float* gates, int64_t gate_stride, const float* bias_i,
+                                 const float* bias_f, float cap, float q_scale, float* memory, float* peak, float* num,
+                                 float* nq, float* peaks_out, const int32_t* q_start, const int32_t* seq_lens,
+                                 const int32_t* slots, int R, int H, int D, int V, int n_slots, int* err, cudaStream_t stream) {
+    constexpr int COLS = MC_WARPS * 4 * CPT, VEC = 16 / (int)sizeof(T);
+    constexpr int smem = 2 * (2 * MC_TOKENS * NI * 4 * MC_LANES + MC_TOKENS * COLS + 5 * MC_TOKENS) * 4;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(matrix_cell_kernel<T, NI, CPT>, smem, opted)) return rc_smem;
+    // rows of q, k and v are fetched 16 bytes at a time where every head's rows start on such a boundary
+    const int wide = D % VEC == 0 && V % VEC == 0 && stride % VEC == 0 && ((uintptr_t)qkv & 15) == 0;
+    const dim3 grid((V + 1 + COLS - 1) / COLS, H, R);
+    ss_launch(matrix_cell_kernel<T, NI, CPT>, grid, dim3(MC_THREADS), smem, stream, (const T*)qkv, stride, gates, gate_stride,
+              bias_i, bias_f, cap, q_scale, memory, peak, num, nq, peaks_out, q_start, seq_lens, slots, H, D, V, n_slots, wide,
+              err);
+    return SS_LAUNCH_CHECK();
 }
 
 template <typename T>
@@ -239,16 +419,17 @@ static int launch_matrix_cell(const void* qkv, int64_t stride, const float* gate
                               const float* bias_f, float cap, float q_scale, float* memory, float* peak, float* num, float* nq,
                               float* peaks_out, const int32_t* q_start, const int32_t* seq_lens, const int32_t* slots, int R,
                               int H, int D, int V, int n_slots, int* err, cudaStream_t stream) {
-    const dim3 grid((V + 1 + MC_COLS - 1) / MC_COLS, H, R);
-    const int smem = (2 * MC_TOKENS * D + MC_TOKENS * MC_COLS + 5 * MC_TOKENS) * 4;
-#define CELL_LAUNCH(DPL)                                                                                                   \
-    ss_launch(matrix_cell_kernel<T, DPL>, grid, dim3(MC_THREADS), smem, stream, (const T*)qkv, stride, gates, gate_stride,  \
-              bias_i, bias_f, cap, q_scale, memory, peak, num, nq, peaks_out, q_start, seq_lens, slots, H, D, V, n_slots, err)
-    if (D <= 8 * MC_LANES) CELL_LAUNCH(8);
-    else if (D <= 16 * MC_LANES) CELL_LAUNCH(16);
-    else CELL_LAUNCH(32);
+#define CELL_LAUNCH(NI, CPT)                                                                                                \
+    return launch_matrix_cell_as<T, NI, CPT>(qkv, stride, gates, gate_stride, bias_i, bias_f, cap, q_scale, memory, peak, num, \
+                                             nq, peaks_out, q_start, seq_lens, slots, R, H, D, V, n_slots, err, stream)
+    const int rows = 4 * MC_LANES;  // rows of one step over a column's lanes
+    if (D <= rows) CELL_LAUNCH(1, 4);
+    if (D <= 2 * rows) CELL_LAUNCH(2, 4);
+    if (D <= 3 * rows) CELL_LAUNCH(3, 4);
+    if (D <= 4 * rows) CELL_LAUNCH(4, 4);
+    if (D <= 6 * rows) CELL_LAUNCH(6, 2);
+    CELL_LAUNCH(8, 2);
 #undef CELL_LAUNCH
-    return SS_LAUNCH_CHECK();
 }
 
 extern "C" int ss_matrix_cell(const void* qkv, int64_t stride, const float* gates, int64_t gate_stride, const float* bias_i,
@@ -360,11 +541,97 @@ gated_recurrence_kernel(const T* __restrict__ proj, int64_t stride, const float*
     state[(int64_t)slot * W + c] = S;
 }
 
+// The same recurrence over prompt portions, cut in time as well.  S_t = (1 - z_t) S_{t-1} + z_t c_t is linear in S, so a
+// segment of tokens acts on the state it meets as S -> A S + B with A the product of its (1 - z_t) and B its result from
+// zero.  A block: one request, 32 channels (the lanes) and GR_SEGS warps; a tile is GR_SEGS segments of GR_LEN tokens.
+// Every warp loads its segment once (all loads in flight together) and forms (A, B); each thread then chains the
+// segments' (A, B) in order from the state the tile met, which gives it the state in front of its own segment and the
+// state behind the tile; then it walks its segment again from registers with the recurrence as written, and writes.
+// Tokens past the request's end act as A = 1, B = 0.
+#define GR_SEGS 16
+#define GR_LEN 8
+
+template <typename T>
+__global__ void __launch_bounds__(GR_SEGS * 32)
+gated_recurrence_portions_kernel(const T* __restrict__ proj, int64_t stride, const float* __restrict__ bias,
+                                 float* __restrict__ state, T* __restrict__ out, const int32_t* __restrict__ q_start,
+                                 const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ slots, int W, int n_slots,
+                                 int* err) {
+    pdl_wait();
+    __shared__ float As[2][GR_SEGS][32], Bs[2][GR_SEGS][32];
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const int r = blockIdx.y, c = blockIdx.x * 32 + lane;
+    const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
+    if (q_len <= 0 || seq_lens[r] <= 0) return;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        return;
+    }
+    const bool live = c < W;
+    float S_tile = live ? state[(int64_t)slot * W + c] : 0.f;
+    const float bz = (bias && live) ? bias[c] : 0.f, bu = (bias && live) ? bias[W + c] : 0.f;
+    const T* src = proj + (int64_t)q0 * stride + (live ? c : 0);
+    int parity = 0;
+    for (int tile0 = 0; tile0 < q_len; tile0 += GR_SEGS * GR_LEN, parity ^= 1) {
+        const int first = tile0 + seg * GR_LEN;
+        float zr[GR_LEN], ur[GR_LEN], gr[GR_LEN];
+#pragma unroll
+        for (int a = 0; a < GR_LEN; ++a) {
+            const bool ok = live && first + a < q_len;
+            const T* p = src + (int64_t)(first + a) * stride;
+            zr[a] = ok ? to_float(p[0]) : 0.f;
+            ur[a] = ok ? to_float(p[W]) : 0.f;
+            gr[a] = ok ? to_float(p[2 * W]) : 0.f;
+        }
+        float A = 1.f, B = 0.f;
+#pragma unroll
+        for (int a = 0; a < GR_LEN; ++a) {
+            const bool ok = first + a < q_len;
+            const float z = ok ? sigmoid_exact(zr[a] + bz) : 0.f, u = ur[a] + bu;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_exact(u);
+            zr[a] = z;
+            ur[a] = cand;
+            A *= 1.0f - z;
+            B = fmaf(z, cand, (1.0f - z) * B);
+        }
+        As[parity][seg][lane] = A;
+        Bs[parity][seg][lane] = B;
+        __syncthreads();  // one barrier a tile: the next tile writes the other pair of tables
+        float S = S_tile, S_in = S_tile;
+#pragma unroll
+        for (int s = 0; s < GR_SEGS; ++s) {
+            if (s == seg) S_in = S;
+            S = fmaf(As[parity][s][lane], S, Bs[parity][s][lane]);
+        }
+        S_tile = S;
+        S = S_in;
+#pragma unroll
+        for (int a = 0; a < GR_LEN; ++a) {
+            if (!live || first + a >= q_len) break;
+            S = fmaf(zr[a], ur[a], (1.0f - zr[a]) * S);
+            const float g = gr[a];
+            out[(int64_t)(q0 + first + a) * W + c] = from_float<T>(S * (g / (1.0f + expf(-g))));
+        }
+    }
+    if (live && seg == 0) state[(int64_t)slot * W + c] = S_tile;
+}
+
 extern "C" int ss_gated_recurrence(const void* proj, int64_t stride, const float* bias, float* state, void* out,
                                    const int32_t* q_start,
                                    const int32_t* seq_lens, const int32_t* slots, int R, int W, int n_slots, int dtype, int* err,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, int portions) {
     if (R <= 0 || W <= 0) return 0;
+    if (portions) {  // some request brings more than a few tokens
+        const dim3 tiles((W + 31) / 32, R);
+        if (dtype == SS_BF16)
+            ss_launch(gated_recurrence_portions_kernel<bf16>, tiles, dim3(GR_SEGS * 32), 0, stream, (const bf16*)proj, stride,
+                      bias, state, (bf16*)out, q_start, seq_lens, slots, W, n_slots, err);
+        else
+            ss_launch(gated_recurrence_portions_kernel<float>, tiles, dim3(GR_SEGS * 32), 0, stream, (const float*)proj, stride,
+                      bias, state, (float*)out, q_start, seq_lens, slots, W, n_slots, err);
+        return SS_LAUNCH_CHECK();
+    }
     const dim3 grid((W + 127) / 128, R);
     if (dtype == SS_BF16)
         ss_launch(gated_recurrence_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, bias, state,
@@ -390,6 +657,13 @@ xielu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, float a, 
     }
 }
 
+// exp(z) - 1 - z for z <= 0, to a few 1e-7 of max(z^2 / 2, 1e-7): a series near zero, where the subtraction would
+// cancel, and the fast exponential elsewhere.  For results that are rounded to bfloat16.
+__device__ __forceinline__ float exp_tail(float z) {
+    const float series = z * z * fmaf(z, fmaf(z, fmaf(z, fmaf(z, 1.f / 720.f, 1.f / 120.f), 1.f / 24.f), 1.f / 6.f), 0.5f);
+    return z > -0.25f ? series : (__expf(z) - 1.f) - z;
+}
+
 // bfloat16, eight elements a thread (n a multiple of 8, both pointers on 16-byte boundaries)
 __global__ void __launch_bounds__(256)
 xielu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t n8, float a, float b) {
@@ -401,8 +675,8 @@ xielu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float z0 = __uint_as_float(w[e] << 16), z1 = __uint_as_float(w[e] & 0xffff0000u);
-            const float y0 = z0 > 0.f ? fmaf(a * z0, z0, 0.5f * z0) : fmaf(b, expm1f(z0) - z0, 0.5f * z0);
-            const float y1 = z1 > 0.f ? fmaf(a * z1, z1, 0.5f * z1) : fmaf(b, expm1f(z1) - z1, 0.5f * z1);
+            const float y0 = z0 > 0.f ? fmaf(a * z0, z0, 0.5f * z0) : fmaf(b, exp_tail(z0), 0.5f * z0);
+            const float y1 = z1 > 0.f ? fmaf(a * z1, z1, 0.5f * z1) : fmaf(b, exp_tail(z1), 0.5f * z1);
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(y0, y1);
             o[e] = *reinterpret_cast<const uint32_t*>(&h2);
         }
@@ -513,7 +787,8 @@ extern "C" int ss_latent_rows(const void* down, int64_t stride, const int32_t* p
 // x_head apart, out rows out_stride apart and heads out_head apart; float32 accumulation in the order of i.
 // `turn` > 0: out[row][h][0 .. turn) takes the `turn` elements x[row][h][I .. I + turn) rotated by the row's position
 // (pairs (i, i + turn / 2)); the product's outputs start at column `turn`, and columns from turn + O to `pad_to`
-// are zeroed.  `scale_col` >= 0: f = sigmoid(gates[row][scale_col + h]).
+// are zeroed.  `scale_col` >= 0: f = sigmoid(gates[row][scale_col + h]).  With w null the product is already in
+// `out` (a library's batched product wrote it): the kernel rotates, zeroes the padding and multiplies by f in place.
 // A block: HP_ROWS rows of one head; threads over o.
 #define HP_ROWS 8
 
@@ -533,8 +808,16 @@ head_product_kernel(const T* __restrict__ x, int64_t x_stride, int x_head, const
         hp_smem[idx] = rr < rows ? to_float(x[(int64_t)(row0 + rr) * x_stride + (int64_t)h * x_head + i]) : 0.f;
     }
     __syncthreads();
+    if (w == nullptr && scale_col >= 0) {
+        for (int idx = tid; idx < rows * O; idx += blockDim.x) {
+            const int rr = idx / O, o = idx - rr * O;
+            const float f = sigmoid_exact(to_float(gates[(int64_t)(row0 + rr) * gate_stride + scale_col + h]));
+            T* dst = out + (int64_t)(row0 + rr) * out_stride + (int64_t)h * out_head + turn + o;
+            *dst = from_float<T>(to_float(*dst) * f);
+        }
+    }
     const T* wh = w + (int64_t)h * I * O;
-    for (int o = tid; o < O; o += blockDim.x) {
+    for (int o = tid; w != nullptr && o < O; o += blockDim.x) {
         float acc[HP_ROWS];
 #pragma unroll
         for (int rr = 0; rr < HP_ROWS; ++rr) acc[rr] = 0.f;

@@ -87,7 +87,7 @@ _OPS_SIGNATURES = {
     "ss_cell_output": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float,
                        c_int, c_void_p],
     "ss_gated_recurrence": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                            c_int, c_void_p, c_void_p],
+                            c_int, c_void_p, c_void_p, c_int],
     "ss_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
     "ss_latent_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_void_p],
@@ -1787,11 +1787,18 @@ def cell_output(num: torch.Tensor, nq: torch.Tensor, peaks: torch.Tensor, weight
     return out
 
 
-def gated_recurrence(proj: torch.Tensor, width: int, state: torch.Tensor, ctx, bias: torch.Tensor | None = None) -> torch.Tensor:
+def gated_recurrence(proj: torch.Tensor, width: int, state: torch.Tensor, ctx, bias: torch.Tensor | None = None,
+                     portions: bool | None = None) -> torch.Tensor:
     """A gated recurrence per channel over each request's tokens, continued from and left in ``state`` (float32
     [slots, width]).  A row of ``proj`` is [z | u | g], ``width`` each; ``bias`` (float32 [2 width]) is added to z and u
     in float32.  ``z' = sigmoid(z)``; the candidate is ``u + 1/2`` where ``u >= 0`` and ``sigmoid(u)`` below;
-    ``S <- (1 - z') S + z' candidate``; returns ``S silu(g)`` [N, width] in the dtype of ``proj``."""
+    ``S <- (1 - z') S + z' candidate``; returns ``S silu(g)`` [N, width] in the dtype of ``proj``.
+
+    ``portions`` (default: every step that is not decode-only) runs the kernel that also cuts a request's tokens into
+    segments: a segment acts on the state in front of it as ``S -> A S + B``, the segments' (A, B) are chained in order,
+    and each segment is then walked from its own starting state.  Otherwise a thread walks all rows of a channel."""
+    if portions is None:
+        portions = not ctx.is_decode_only
     _need(proj, None, "projection")
     _need(state, torch.float32, "state")
     if bias is not None:
@@ -1804,7 +1811,8 @@ def gated_recurrence(proj: torch.Tensor, width: int, state: torch.Tensor, ctx, b
     _check(ops_library().ss_gated_recurrence(proj.data_ptr(), proj.stride(0), _ptr(bias), state.data_ptr(), out.data_ptr(),
                                              ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
                                              ctx.num_requests, width, state.shape[0], _code(proj.dtype),
-                                             error_word(proj.device).data_ptr(), _stream()), "gated_recurrence")
+                                             error_word(proj.device).data_ptr(), _stream(), int(bool(portions))),
+           "gated_recurrence")
     return out
 
 
@@ -1851,6 +1859,9 @@ def latent_rows(down: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor
     return cq
 
 
+HEAD_PRODUCT_LIBRARY_ROWS = 128  # rows from which the per-head products go to the library's batched product
+
+
 def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, *, turn: int = 0,
                  pad_to: int | None = None, positions: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None,
                  mscale: float = 1.0, gates: torch.Tensor | None = None) -> torch.Tensor:
@@ -1858,7 +1869,11 @@ def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.
     of a row of ``x`` starting at column ``h * x_head`` and of ``out`` at ``h * out_head``; float32 accumulation in the
     order of i.  ``turn`` > 0: the ``turn`` elements of x behind the I inputs are rotated by the row's position (pairs
     (i, i + turn / 2), ``inv_freq`` None: copied) into ``out[n, h, :turn]``.  Columns from ``turn + O`` to ``pad_to`` are
-    zeroed.  ``gates`` (a view [N, H] in the dtype of x, unit inner stride): ``f = sigmoid(gates[n, h])``, else 1."""
+    zeroed.  ``gates`` (a view [N, H] in the dtype of x, unit inner stride): ``f = sigmoid(gates[n, h])``, else 1.
+
+    bfloat16 with at least ``HEAD_PRODUCT_LIBRARY_ROWS`` rows (prompt portions): the products are one batched library
+    matrix product over strided views of ``x`` and ``out`` (as `linear` falls to the library product), and this
+    package's kernel then only rotates, zeroes the padding and applies ``f`` in place."""
     _need(x, None, "x")
     _need(weight, x.dtype, "weights per head")
     _need(out, x.dtype, "output")
@@ -1877,7 +1892,14 @@ def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.
         gate_ptr, gate_stride = gates.data_ptr(), gates.stride(0)
     else:
         scale_col = -1
-    _check(ops_library().ss_head_product(x.data_ptr(), x.stride(0), int(x_head), weight.data_ptr(), out.data_ptr(),
+    weight_ptr = weight.data_ptr()
+    if x.dtype == torch.bfloat16 and n >= HEAD_PRODUCT_LIBRARY_ROWS:
+        torch.bmm(x.as_strided((h, n, i), (int(x_head), x.stride(0), 1)), weight,
+                  out=out.as_strided((h, n, o), (int(out_head), out.stride(0), 1), out.storage_offset() + int(turn)))
+        if not turn and pad_to == o and gates is None:
+            return out
+        weight_ptr = None
+    _check(ops_library().ss_head_product(x.data_ptr(), x.stride(0), int(x_head), weight_ptr, out.data_ptr(),
                                          out.stride(0), int(out_head), n, h, i, o, int(turn), pad_to, _ptr(positions),
                                          _ptr(inv_freq), float(mscale), gate_ptr, gate_stride, scale_col, _code(x.dtype),
                                          _stream()), "head_product")
