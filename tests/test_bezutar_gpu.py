@@ -334,6 +334,11 @@ def test_model_structure_follows_the_configuration():
 CUTS = ([[("a", 37), ("b", 6)]],
         [[("a", 16)], [("a", 1), ("b", 2)], [("a", 17), ("b", 1)], [("a", 2), ("b", 3)], [("a", 1)]],
         [[("a", 2), ("b", 2)]] + [[("a", 1), ("b", 1)]] * 4 + [[("a", 31)]])
+# portions that cross the recurrences' batches of 32 and tiles of 128 tokens, cut at, just before and just behind them
+LONG_CUTS = ([[("a", 300), ("b", 131)]],
+             [[("a", 127), ("b", 1)], [("a", 2), ("b", 129)], [("a", 33), ("b", 1)], [("a", 138)]],
+             [[("a", 128)], [("a", 129), ("b", 64)], [("a", 43), ("b", 67)]])
+SPANS = {"short": ({"a": 37, "b": 6}, CUTS), "long": ({"a": 300, "b": 131}, LONG_CUTS)}
 
 
 @pytest.mark.gpu
@@ -412,15 +417,16 @@ def cell_weights(g, width, heads, dim, vdim, cap):
 @pytest.mark.gpu
 @pytest.mark.parametrize("heads, dim, vdim, cap, dtype", [(3, 20, 24, 10.0, torch.float32), (1, 136, 40, 4.0, torch.float32), (5, 8, 16, 15.0, torch.float32),
                                                         (2, 256, 72, 2.0, torch.float32), (4, 1, 1, 7.0, torch.float32), (2, 64, 128, 15.0, torch.bfloat16),
-                                                        (6, 32, 8, 3.0, torch.bfloat16)])
-def test_matrix_memory_against_the_literal_loop_however_it_is_cut(heads, dim, vdim, cap, dtype):
+                                                        (6, 32, 8, 3.0, torch.bfloat16), (2, 44, 30, 6.0, torch.bfloat16)])
+@pytest.mark.parametrize("spans", ["short", "long"])
+def test_matrix_memory_against_the_literal_loop_however_it_is_cut(heads, dim, vdim, cap, dtype, spans):
     """Raw gates run far beyond the cap on both sides, so that the cap, the running maximum's start at 0 and the lower
     bound exp(-m) of the denominator all take part; the state slots start as their last owners left them.  The literal
     loop reads the projections as the kernel does (rounded to bfloat16 where it runs in bfloat16)."""
     from slipstream_b200 import ops
     g = torch.Generator().manual_seed(heads * 1000 + dim + vdim)
     width = 48
-    lens, slots = {"a": 37, "b": 6}, {"a": 1, "b": 3}
+    (lens, cuts), slots = SPANS[spans], {"a": 1, "b": 3}
     w = cell_weights(g, width, heads, dim, vdim, cap)
     m = {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
     x = {k: torch.randn(n, width, generator=g) * 1.5 for k, n in lens.items()}
@@ -440,7 +446,7 @@ def test_matrix_memory_against_the_literal_loop_however_it_is_cut(heads, dim, vd
     assert max(spread) > 1.2 * cap and min(spread) < -1.2 * cap
     tol = 2e-4 if dtype == torch.float32 else 2e-2
     g0 = heads * (2 * dim + vdim)
-    for plan in CUTS:
+    for plan in cuts:
         memory = torch.full((4, heads, vdim + 1, dim), 3.0, device=DEV)
         peak = torch.full((4, heads), -2.0, device=DEV)
         for s in slots.values():
@@ -481,11 +487,14 @@ def _cell_from_projections(q, k, v, gate, raw_gates, m, norm_weight, eps):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("width, dtype", [(90, torch.float32), (300, torch.float32), (1, torch.float32), (48, torch.bfloat16), (136, torch.bfloat16)])
-def test_gated_recurrence_against_the_literal_loop_however_it_is_cut(width, dtype):
+@pytest.mark.parametrize("spans", ["short", "long"])
+def test_gated_recurrence_against_the_literal_loop_however_it_is_cut(width, dtype, spans):
+    """Steps of single tokens run the kernel that walks a channel's rows in order; every other step the one that also
+    cuts a request's tokens into segments and chains what each segment does to the state in front of it."""
     from slipstream_b200 import ops
     g = torch.Generator().manual_seed(width)
     hidden = 40
-    lens, slots = {"a": 37, "b": 6}, {"a": 1, "b": 3}
+    (lens, cuts), slots = SPANS[spans], {"a": 1, "b": 3}
     lin = lambda rows, cols, gain=1.0: torch.randn(rows, cols, generator=g) * gain * cols ** -0.5  # noqa: E731
     w = {"r.z": lin(width, hidden, 2.0), "r.x": lin(width, hidden, 2.0), "r.g": lin(width, hidden), "r.o": torch.eye(width),
          "r.z.b": torch.randn(width, generator=g) - 1.0, "r.x.b": torch.randn(width, generator=g) * 0.5}
@@ -504,7 +513,7 @@ def test_gated_recurrence_against_the_literal_loop_however_it_is_cut(width, dtyp
         if dtype == torch.float32:
             assert torch.allclose(want[k], plain.gated_recurrence(x[k].double(), w, "r", {"width": width}), atol=1e-4, rtol=1e-4)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
-    for plan in CUTS:
+    for plan in cuts:
         state = torch.full((4, width), 3.0, device=DEV)
         for s in slots.values():
             state[s].zero_()
@@ -589,16 +598,18 @@ def test_latents_are_normed_rotated_and_written_to_their_pages(q_rank, kv_rank, 
 @pytest.mark.parametrize("heads, inputs, outputs, turn, dtype", [(3, 24, 36, 8, torch.float32), (5, 16, 36, 8, torch.float32), (2, 32, 112, 16, torch.float32),
                                                                (3, 8, 24, 24, torch.float32), (4, 44, 20, 0, torch.float32), (8, 64, 64, 16, torch.bfloat16),
                                                                (1, 128, 200, 56, torch.bfloat16)])
-def test_products_per_head_with_rotation_and_gate(heads, inputs, outputs, turn, dtype):
+@pytest.mark.parametrize("n", [7, 150])
+def test_products_per_head_with_rotation_and_gate(heads, inputs, outputs, turn, dtype, n):
     """Queries carried into the latent space ([rotated part | product | zeros] per head) and latent-sized outputs
-    carried up to values under a gate per head."""
+    carried up to values under a gate per head.  With 150 rows the bfloat16 products are the library's batched product
+    over strided views, and the kernel only rotates, pads and gates."""
     from slipstream_b200 import ops
     g = torch.Generator().manual_seed(heads * 100 + inputs)
-    n, base = 7, 900.0
+    base = 900.0
     x_head = inputs + turn
     x = torch.randn(n, heads * x_head + 3, generator=g).to(dtype)
     w = (torch.randn(heads, inputs, outputs, generator=g) * inputs ** -0.5).to(dtype)
-    positions = torch.tensor([0, 1, 17, 300, 2, 45, 1000], dtype=torch.int32)
+    positions = torch.tensor(([0, 1, 17, 300, 2, 45, 1000] * 22)[:n], dtype=torch.int32)
     rot = {"base": base, "dims": turn}
     pad = -(-(turn + outputs) // 16) * 16
     out = torch.full((n, heads * pad), 5.0, dtype=dtype, device=DEV)
