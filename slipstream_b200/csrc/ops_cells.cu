@@ -132,7 +132,7 @@ extern "C" int ss_embed_sum(const int32_t* tokens, const int32_t* positions, con
 #define MC_LANES 8
 #define MC_TOKENS 32  // a lane of the staging warp a token
 #define MC_GROUP 4
-#define MC_WARPS 2
+#define MC_WARPS 4
 #define MC_THREADS ((MC_WARPS + 3) * 32)
 static_assert(MC_TOKENS == 32 && MC_TOKENS % MC_GROUP == 0, "the gates of a batch are one warp wide");
 
@@ -423,10 +423,10 @@ static int launch_matrix_cell(const void* qkv, int64_t stride, const float* gate
     return launch_matrix_cell_as<T, NI, CPT>(qkv, stride, gates, gate_stride, bias_i, bias_f, cap, q_scale, memory, peak, num, \
                                              nq, peaks_out, q_start, seq_lens, slots, R, H, D, V, n_slots, err, stream)
     const int rows = 4 * MC_LANES;  // rows of one step over a column's lanes
-    if (D <= rows) CELL_LAUNCH(1, 4);
-    if (D <= 2 * rows) CELL_LAUNCH(2, 4);
-    if (D <= 3 * rows) CELL_LAUNCH(3, 4);
-    if (D <= 4 * rows) CELL_LAUNCH(4, 4);
+    if (D <= rows) CELL_LAUNCH(1, 2);
+    if (D <= 2 * rows) CELL_LAUNCH(2, 2);
+    if (D <= 3 * rows) CELL_LAUNCH(3, 2);
+    if (D <= 4 * rows) CELL_LAUNCH(4, 2);
     if (D <= 6 * rows) CELL_LAUNCH(6, 2);
     CELL_LAUNCH(8, 2);
 #undef CELL_LAUNCH
@@ -544,7 +544,7 @@ gated_recurrence_kernel(const T* __restrict__ proj, int64_t stride, const float*
 // The same recurrence over prompt portions, cut in time as well.  S_t = (1 - z_t) S_{t-1} + z_t c_t is linear in S, so a
 // segment of tokens acts on the state it meets as S -> A S + B with A the product of its (1 - z_t) and B its result from
 // zero.  A block: one request, 32 channels (the lanes) and GR_SEGS warps; a tile is GR_SEGS segments of GR_LEN tokens.
-// Every warp loads its segment once (all loads in flight together) and forms (A, B); each thread then chains the
+// Every warp loads its segment once (all loads in flight together, a tile ahead of their use) and forms (A, B); each thread then chains the
 // segments' (A, B) in order from the state the tile met, which gives it the state in front of its own segment and the
 // state behind the tile; then it walks its segment again from registers with the recurrence as written, and writes.
 // Tokens past the request's end act as A = 1, B = 0.
@@ -573,17 +573,22 @@ gated_recurrence_portions_kernel(const T* __restrict__ proj, int64_t stride, con
     const float bz = (bias && live) ? bias[c] : 0.f, bu = (bias && live) ? bias[W + c] : 0.f;
     const T* src = proj + (int64_t)q0 * stride + (live ? c : 0);
     int parity = 0;
-    for (int tile0 = 0; tile0 < q_len; tile0 += GR_SEGS * GR_LEN, parity ^= 1) {
-        const int first = tile0 + seg * GR_LEN;
-        float zr[GR_LEN], ur[GR_LEN], gr[GR_LEN];
+    float zr[GR_LEN], ur[GR_LEN], gr[GR_LEN];
+    auto fetch = [&](int first, float (&z)[GR_LEN], float (&u)[GR_LEN], float (&g)[GR_LEN]) {
 #pragma unroll
         for (int a = 0; a < GR_LEN; ++a) {
             const bool ok = live && first + a < q_len;
             const T* p = src + (int64_t)(first + a) * stride;
-            zr[a] = ok ? to_float(p[0]) : 0.f;
-            ur[a] = ok ? to_float(p[W]) : 0.f;
-            gr[a] = ok ? to_float(p[2 * W]) : 0.f;
+            z[a] = ok ? to_float(p[0]) : 0.f;
+            u[a] = ok ? to_float(p[W]) : 0.f;
+            g[a] = ok ? to_float(p[2 * W]) : 0.f;
         }
+    };
+    fetch(seg * GR_LEN, zr, ur, gr);
+    for (int tile0 = 0; tile0 < q_len; tile0 += GR_SEGS * GR_LEN, parity ^= 1) {
+        const int first = tile0 + seg * GR_LEN;
+        float zn[GR_LEN], un[GR_LEN], gn[GR_LEN];  // the next tile's rows are fetched while this one is walked
+        fetch(first + GR_SEGS * GR_LEN, zn, un, gn);
         float A = 1.f, B = 0.f;
 #pragma unroll
         for (int a = 0; a < GR_LEN; ++a) {
@@ -612,6 +617,12 @@ gated_recurrence_portions_kernel(const T* __restrict__ proj, int64_t stride, con
             S = fmaf(zr[a], ur[a], (1.0f - zr[a]) * S);
             const float g = gr[a];
             out[(int64_t)(q0 + first + a) * W + c] = from_float<T>(S * (g / (1.0f + expf(-g))));
+        }
+#pragma unroll
+        for (int a = 0; a < GR_LEN; ++a) {
+            zr[a] = zn[a];
+            ur[a] = un[a];
+            gr[a] = gn[a];
         }
     }
     if (live && seg == 0) state[(int64_t)slot * W + c] = S_tile;
