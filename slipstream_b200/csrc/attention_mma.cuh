@@ -386,7 +386,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
     const int kt_lo = kt_first + slice * per, kt_hi = min(kt_last, kt_lo + per - 1);
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (sinks && slice == 0 && warp == 0) {  // the sink's term counts once: in the first warp of the first slice
+    if (sinks && slice == 0 && warp == 0) {  // the sink's term is added one time: by the first warp of the first slice
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = (lane >> 2) + h * 8;

@@ -10,7 +10,7 @@
 // in the request; window 0 = all earlier keys), which is the packed-index causal
 // rule of slipstream/models/layers/attention.py:46-51; scores are scaled after the
 // dot product and softmax is float32 as in :64-88.  `sinks` (float32, one per query head, or null): the softmax's
-// denominator also holds exp(sinks[h]), a term without key or value that is not scaled.  Replaces the gather + eager
+// denominator also holds exp(sinks[h]), a term of its own with neither key nor value, which the scale does not touch.  Replaces the gather + eager
 // loop of slipstream/kernels/attention_ref.py:68-89 and the Triton decode kernel
 // slipstream/kernels/triton_paged.py:97-206.
 //
@@ -68,7 +68,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
 #pragma unroll
     for (int i = 0; i < ATT_RPW; ++i) {
         lowest[i] = key_floor(pos0 + w * ATT_RPW + i, window);
-        // a sink: one more term exp(sinks[h]) in the row's denominator, with no key and no value; it counts once
+        // a sink: one more term exp(sinks[h]) in the row's denominator, with neither key nor value, added one time
         m[i] = sinks ? sinks[h] : -INFINITY;
         l[i] = sinks ? 1.f : 0.f;
 #pragma unroll

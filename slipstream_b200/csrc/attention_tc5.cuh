@@ -471,7 +471,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (splits == 1) {
             if (ok) {
-                // a sink has no key and no value and counts once: its term joins the sum, in the sum's own units
+                // the sink's term joins the row's sum one time, in the sum's own units
                 if (a.sinks && valid)
                     l = m_ref == -INFINITY ? 1.f : l + ex2(a.sinks[kvh * G + g] * 1.4426950408889634f - m_ref);
                 const float inv = l > 0.f ? 1.f / l : 0.f;

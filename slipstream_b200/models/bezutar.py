@@ -4,7 +4,7 @@ tensor names.
 Embedding: the sum of the token's row (``embed``), a hashed row of token pairs (``bigram``, when the configuration has
 ``embedding.bigram``) and a learned position row (``pos``, when it has ``max_positions``), copied into every residual
 stream.  Per layer ``l<i>`` a `HyperConnectionBlock` (``l<i>.hc1.*`` around the mixer, ``l<i>.hc2.*`` around the
-feed-forward; without ``streams`` the plain residual sum) whose norms hold their weights around zero
+feed-forward; without ``streams`` the plain residual sum) whose norms store their weights as the difference from one
 (``l<i>.norm1``, ``l<i>.norm2``).  The mixer, by ``type``:
 
 * ``mlstm``: a `MatrixMemoryMixer` (``l<i>.mix.{q,k,v,g,o,norm,i,i.b,f,f.b}``);

@@ -566,7 +566,7 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
     ``out`` is [N, n_q * D].  ``tile_req`` / ``tile_q0`` list tiles of 16 consecutive query tokens
     of one request (request index, first token within the request's rows of this step).
     ``sinks`` (in this entry point and the two mma.sync ones; float32 [n_q]): the softmax's denominator of head h also
-    holds ``exp(sinks[h])``, a term that has no key and no value and is not scaled."""
+    holds ``exp(sinks[h])``, a term of its own with neither key nor value, which the scale does not touch."""
     _need(out, q.dtype, "attention output")
     _check_sinks(sinks, n_q)
     _need(kv, q.dtype, "kv pages")

@@ -46,7 +46,7 @@ class SummedEmbedding(Embedding):
     * with ``pair_hash`` = (buckets, mul_prev, mul_cur): row ``(previous * mul_prev + token * mul_cur) mod buckets`` of
       a table of ``buckets + 1`` rows, whose last row serves a request's first token.  The previous token of a step's
       first row is per-request state (``last_token``, an int32 per slot), so a request may be cut anywhere;
-    * with ``positions``: row ``position`` of a learned table of that many rows (not scaled).
+    * with ``positions``: row ``position`` of a learned table of that many rows (added as it is).
 
     ``copies``: how many residual streams the model keeps (see `TokenEmbedding`).  ``names``: the checkpoint's tensor
     names by role (token, pair, position)."""

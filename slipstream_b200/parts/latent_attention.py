@@ -8,7 +8,7 @@ With H heads of ``dim`` unrotated and ``rot_dim`` rotated query/key elements and
     k_h^plain = W_uk,h c,   v_h = W_uv,h c
     score_h(i, j) = (q_h^plain(i) . k_h^plain(j) + rotate(q_h^turn(i), i) . s(j)) * scale,   j <= i
 
-a softmax whose denominator also holds ``exp(sink_h)`` (a learned number per head without key or value, not scaled),
+a softmax whose denominator also holds ``exp(sink_h)`` (one learned number per head with neither key nor value, which the scale does not touch),
 each head's output times ``sigmoid(w_g,h . x)``, and the output projection on the concatenated heads.
 
 How it runs.  The products with W_uk and W_uv move to the query's side, so that the cache holds every token once,

@@ -54,7 +54,7 @@ class ConnectedNorm(Norm):
 
     ``tensor``: the norm's weight vector.  ``connection``: prefix of the branch's ``.in``, ``.out`` and ``.mix``
     tensors; None stands for in = 1 (the plain sum) and, for `write_of`, out = 1 and mix = identity, which needs
-    no tensors.  ``offset``: the stored weight vector lies around zero and the norm multiplies by ``offset + weight``
+    no tensors.  ``offset``: the tensor holds the weight's difference from ``offset`` and the norm multiplies by ``offset + weight``
     (formed once, in float32).  All arithmetic is float32; the result is rounded once."""
 
     cuda_graph_safe = True

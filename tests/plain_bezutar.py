@@ -55,7 +55,7 @@ def embed(config: dict, w: dict, tokens: list[int]) -> torch.Tensor:
 # --------------------------------------------------------------------------- norms, streams, the short convolution
 
 def offset_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """RMS norm whose stored weight lies around zero."""
+    """RMS norm whose tensor holds the weight's difference from one."""
     return rms_unit(x, eps) * (1.0 + weight.to(F64))
 
 
