@@ -155,8 +155,9 @@ extern "C" int ss_round_stream(const float* in, void* out, int64_t n, cudaStream
 // input(t - (T - 1 - j))), where inputs in front of the step's first row come from the request's state
 // [slot][T - 1][C] (float32; index T - 2 is the newest) and inputs in front of the request's first token are the
 // zeros a fresh state holds.  `fused_update`: every request brings one token and the thread that read the state
-// also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.  `plus_input`: the
-// result is input + (bias +) convolution with no activation instead (a convolution on a branch's input).
+// also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.  `plus_input` 1: the
+// result is input + (bias +) convolution with no activation instead (a convolution on a branch's input); 2: bias +
+// convolution with no activation.
 #define CONV_MAX_TAPS 8
 #define CONV_ROWS 32
 // A thread takes one channel over CONV_ROWS consecutive rows and keeps the channel's last T - 1 inputs in
@@ -211,7 +212,7 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS; ++j)  // (no register array is indexed by a run-time value)
             if (j <= back) acc = fmaf(w[j], j < back ? x[j] : cur, acc);
-        out[(int64_t)row * C + c] = from_float<T>(plus_input ? cur + acc : silu_exact(acc));
+        out[(int64_t)row * C + c] = from_float<T>(plus_input == 1 ? cur + acc : (plus_input == 2 ? acc : silu_exact(acc)));
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < back) x[j] = j + 1 < back ? x[j + 1] : cur;
@@ -298,7 +299,7 @@ conv_silu_bf16x8_kernel(const bf16* __restrict__ proj, int64_t stride, int col0,
 #pragma unroll
                 for (int j = 0; j <= MAXB; ++j)
                     if (j <= back) acc = fmaf(w[e + d][j], j < back ? x[e + d][j < MAXB ? j : 0] : cur[e + d], acc);
-                o2[d] = plus_input ? cur[e + d] + acc : silu_exact(acc);
+                o2[d] = plus_input == 1 ? cur[e + d] + acc : (plus_input == 2 ? acc : silu_exact(acc));
             }
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(o2[0], o2[1]);
             packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
@@ -674,36 +675,92 @@ extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t d
 
 // ---------------------------------------------------------------- router of the routed experts
 //
-// z = W_router x in float32 (x and W in the compute type), scores s = sigmoid(z) in float32, the `top` largest
-// scores chosen (ties, which saturated scores make real: the lower index); ids[token][k] the chosen expert,
-// w[token][k] = its score, or, with `renormalize`, that divided by the sum over the chosen.  A block per token.
+// z = W_router x in float32 (x and W in the compute type); scores s = sigmoid(z), or, with `softmax`, the softmax of
+// z over all experts; choice scores c = s + correction (no correction: c = s).  With `groups` > 1 the experts form
+// that many equal groups of neighbours, a group's score is its largest choice score, and only experts of the `keep`
+// best groups can be chosen (the others' choice scores count as -infinity).  The `top` largest choice scores are
+// chosen (ties: the lower index); ids[token][k] the chosen expert, w[token][k] = its score s (without the
+// correction), or, with `renormalize`, that divided by the sum over the chosen.  `extra` more rows of W behind the
+// experts' ride along in the product: their logits leave raw in extra_out[token][extra] (a gate that reads the
+// same input, say).  A block per token.
 #define ROUTER_MAX_EXPERTS 1024
 template <typename T>
 __global__ void __launch_bounds__(128)
 router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* __restrict__ ids,
-              float* __restrict__ weights, int hidden, int experts, int top, int renormalize) {
+              float* __restrict__ weights, int hidden, int experts, int top, int renormalize, int softmax,
+              const float* __restrict__ correction, int groups, int keep, float* __restrict__ extra_out, int extra) {
     pdl_wait();
     extern __shared__ float rsm[];
-    float* xs = rsm;              // [hidden]
-    float* z = rsm + hidden;      // [experts]
+    float* xs = rsm;                  // [hidden]
+    float* z = rsm + hidden;          // [experts] scores
+    float* c = z + experts;           // [experts] choice scores
+    float* gb = c + experts;          // [groups] the groups' scores
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < hidden; i += blockDim.x) xs[i] = to_float(x[(int64_t)t * hidden + i]);
     __syncthreads();
-    for (int e = warp; e < experts; e += 4) {
+    for (int e = warp; e < experts + extra; e += 4) {
         const T* w = w_router + (int64_t)e * hidden;
         float acc = 0.f;
         for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(w[i]), xs[i], acc);
         acc = warp_sum(acc);
-        if (lane == 0) z[e] = 1.0f / (1.0f + expf(-acc));  // the score; the choice below is among scores
+        if (lane == 0) {
+            if (e >= experts) extra_out[(int64_t)t * extra + (e - experts)] = acc;
+            else z[e] = softmax ? acc : 1.0f / (1.0f + expf(-acc));  // the choice below is among scores
+        }
     }
     __syncthreads();
     if (warp != 0) return;
+    if (softmax) {
+        float mx = -INFINITY;
+        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < experts; e += 32) {
+            const float p = expf(z[e] - mx);
+            z[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) z[e] = z[e] / sum;
+    }
+    for (int e = lane; e < experts; e += 32) c[e] = z[e] + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    if (groups > 1) {
+        const int per = experts / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, c[e]);
+            gb[g] = m;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep; ++k) {  // the best group that is left, `keep` times; a kept group is marked by NaN
+            float best = -INFINITY;
+            int at = groups;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gb[g];
+                if (v == v && (v > best || at == groups)) { best = v; at = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (oa < groups && (at == groups || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at < groups) gb[at] = __int_as_float(0x7fc00000);
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32) {
+            const float mark = gb[e / per];
+            if (mark == mark) c[e] = -INFINITY;  // its group was not kept
+        }
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = experts;
         for (int e = lane; e < experts; e += 32) {
-            const float v = z[e];
+            const float v = c[e];
             if (v > best) { best = v; at = e; }  // ascending e: the lower index stays on a tie
         }
 #pragma unroll
@@ -712,12 +769,12 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* 
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
-        const float s = best;
+        const float s = at < experts ? z[at] : 0.f;
         total += s;
         if (lane == 0) {
             ids[(int64_t)t * top + k] = at < experts ? at : 0;
             weights[(int64_t)t * top + k] = s;
-            if (at < experts) z[at] = -INFINITY;
+            if (at < experts) c[at] = -INFINITY;
         }
         __syncwarp();
     }
@@ -726,17 +783,20 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* 
 }
 
 extern "C" int ss_router(const void* x, const void* w_router, int32_t* ids, float* weights, int n_tokens, int hidden,
-                         int experts, int top, int renormalize, int dtype, cudaStream_t stream) {
+                         int experts, int top, int renormalize, int dtype, cudaStream_t stream, int softmax,
+                         const float* correction, int groups, int keep, float* extra_out, int extra) {
     if (n_tokens <= 0) return 0;
     if (experts < 1 || experts > ROUTER_MAX_EXPERTS || top < 1 || top > experts) return (int)cudaErrorInvalidValue;
-    const int smem = (hidden + experts) * 4;
+    if (groups < 1 || experts % groups || keep < 1 || keep > groups || extra < 0 || (extra > 0 && !extra_out))
+        return (int)cudaErrorInvalidValue;
+    const int smem = (hidden + 2 * experts + groups) * 4;
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     if (dtype == SS_BF16)
         ss_launch(router_kernel<bf16>, dim3(n_tokens), dim3(128), smem, stream, (const bf16*)x, (const bf16*)w_router, ids,
-                  weights, hidden, experts, top, renormalize);
+                  weights, hidden, experts, top, renormalize, softmax, correction, groups, keep, extra_out, extra);
     else
         ss_launch(router_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)x, (const float*)w_router,
-                  ids, weights, hidden, experts, top, renormalize);
+                  ids, weights, hidden, experts, top, renormalize, softmax, correction, groups, keep, extra_out, extra);
     return SS_LAUNCH_CHECK();
 }
 
@@ -747,11 +807,12 @@ extern "C" int ss_router(const void* x, const void* w_router, int32_t* ids, floa
 // rows: tile_expert[i] (or -1 for a tile that holds nothing), tile_row0[i], tile_rows[i].  The lists have
 // ceil(A / tile) + experts entries, the most any routing needs, so the launch that walks them is the same every
 // step.  One block.  Places within an expert follow the order in which threads arrive; no result depends on it,
-// since every row of a product is computed by itself.
+// since every row of a product is computed by itself.  Experts from `real` on have no weights (experts that hand their
+// input on): their assignments are sorted like the others, their tiles are marked as holding nothing.
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int32_t* __restrict__ tile_expert,
                 int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows, int A, int experts, int tile,
-                int max_tiles, int32_t* __restrict__ place) {
+                int max_tiles, int32_t* __restrict__ place, int real) {
     pdl_wait();
     __shared__ int count[ROUTER_MAX_EXPERTS], start[ROUTER_MAX_EXPERTS], first_tile[ROUTER_MAX_EXPERTS + 1];
     const int tid = threadIdx.x;
@@ -774,7 +835,7 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int
         const int n = count[e];
         for (int i = 0; i * tile < n; ++i) {
             const int at = first_tile[e] + i;
-            tile_expert[at] = e;
+            tile_expert[at] = e < real ? e : -1;  // an expert without weights: its rows keep their places, no product runs
             tile_row0[at] = start[e] + i * tile;
             tile_rows[at] = min(tile, n - i * tile);
         }
@@ -795,22 +856,24 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int
 }
 
 extern "C" int ss_moe_plan(const int32_t* ids, int32_t* perm, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows,
-                           int A, int experts, int tile, int max_tiles, int32_t* place, cudaStream_t stream) {
+                           int A, int experts, int tile, int max_tiles, int32_t* place, cudaStream_t stream, int real) {
     if (A <= 0) return 0;
     if (experts < 1 || experts > ROUTER_MAX_EXPERTS || tile < 1 || max_tiles < (A + tile - 1) / tile + experts)
         return (int)cudaErrorInvalidValue;
     ss_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, perm, tile_expert, tile_row0, tile_rows, A, experts, tile,
-              max_tiles, place);
+              max_tiles, place, real > 0 ? real : experts);
     return SS_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- grouped products on CUDA cores
 //
 // UP:   hidden[s][n] = silu(g) * u,  g = sum_k a_k Wgu[e][n][k],  u = sum_k a_k Wgu[e][ff + n][k],
-//       a = round_T(w[perm[s]] * x[perm[s] / top])   (the weight is on the expert's input)
+//       a = round_T(w[perm[s]] * x[perm[s] / top])   (the weight is on the expert's input; no weights: a = x)
 // DOWN: y[perm[s]][n] = sum_k hidden[s][k] Wd[e][n][k]   (float32 out, one row per assignment)
+// `single` (with the DOWN form, for experts without a gate branch): hidden[s][n] = relu(z)^2, z = sum_k a_k W[e][n][k]
 // for the rows s of the plan's tile blockIdx.x (expert e) and the 64 columns n of blockIdx.y.  float32
 // accumulation in a fixed order.
+__device__ __forceinline__ float relu_square(float z) { return z > 0.f ? z * z : 0.f; }
 #define MG_M 64
 #define MG_N 64
 #define MG_K 16
@@ -819,11 +882,12 @@ __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, const T* __restrict__ W,
                 const int32_t* __restrict__ perm, const int32_t* __restrict__ tile_expert,
                 const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_rows, T* __restrict__ hidden,
-                float* __restrict__ y, int top, int K, int n_out, int run) {
+                float* __restrict__ y, int top, int K, int n_out, int run, int single) {
     pdl_wait();
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     const int row0 = tile_row0[blockIdx.x], rows = tile_rows[blockIdx.x];
+    const bool first = UP || single;  // the product that reads the tokens' rows and writes the hidden rows
     __shared__ float As[MG_K][MG_M + 4];
     __shared__ float Ws[UP ? 2 : 1][MG_K][MG_N + 4];
     __shared__ int src_row[MG_M];
@@ -833,7 +897,7 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
     if (tid < MG_M) {
         const int a = tid < rows ? perm[row0 + tid] : -1;
         src_row[tid] = a;
-        src_w[tid] = (UP && a >= 0) ? weights[a] : 1.f;
+        src_w[tid] = (first && a >= 0 && weights) ? weights[a] : 1.f;
     }
     __syncthreads();
     // UP: W is [experts][2 n_out][K]; DOWN: [experts][n_out][K]
@@ -852,7 +916,7 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
             const int k = k0 + lk + q;
             float a = 0.f;
             if (lr < rows && k < K) {
-                if (UP) a = to_float(from_float<T>(src_w[lr] * to_float(x[(int64_t)(src_row[lr] / top) * K + k])));
+                if (first) a = to_float(from_float<T>(src_w[lr] * to_float(x[(int64_t)(src_row[lr] / top) * K + k])));
                 else a = to_float(x[(int64_t)(row0 + lr) * K + k]);
             }
             As[lk + q][lr] = a;
@@ -889,6 +953,7 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
             const int n = n0 + tx * 4 + j;
             if (n >= n_out) continue;
             if (UP) hidden[(int64_t)(row0 + m) * n_out + n] = from_float<T>(silu_mul<false>(acc[0][i][j], acc[UP ? 1 : 0][i][j]));
+            else if (single) hidden[(int64_t)(row0 + m) * n_out + n] = from_float<T>(relu_square(acc[0][i][j]));
             else y[(int64_t)src_row[m] * n_out + n] = acc[0][i][j];
         }
     }
@@ -896,13 +961,15 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
 
 extern "C" int ss_moe_gemm(const void* x, const float* weights, const void* W, const int32_t* perm,
                            const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* tile_rows, void* hidden,
-                           float* y, int top, int K, int n_out, int max_tiles, int up, int dtype, int run, cudaStream_t stream) {
+                           float* y, int top, int K, int n_out, int max_tiles, int up, int dtype, int run, cudaStream_t stream,
+                           int single) {
     if (max_tiles <= 0) return 0;
     if (up && (run < 1 || n_out % run)) return (int)cudaErrorInvalidValue;
+    if (single && (up || !hidden)) return (int)cudaErrorInvalidValue;
     const dim3 grid(max_tiles, (n_out + MG_N - 1) / MG_N);
 #define MG_GO(T, UP)                                                                                                    \
     ss_launch(moe_gemm_kernel<T, UP>, grid, dim3(256), 0, stream, (const T*)x, weights, (const T*)W, perm, tile_expert,       \
-              tile_row0, tile_rows, (T*)hidden, y, top, K, n_out, run)
+              tile_row0, tile_rows, (T*)hidden, y, top, K, n_out, run, single)
     if (dtype == SS_BF16) { if (up) MG_GO(bf16, true); else MG_GO(bf16, false); }
     else { if (up) MG_GO(float, true); else MG_GO(float, false); }
 #undef MG_GO
@@ -940,7 +1007,7 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, const float* __res
     if (idx >= (int64_t)total * chunks) return;
     const int s = (int)(idx / chunks), c = (int)(idx - (int64_t)s * chunks);
     const int a = perm[s];
-    const float w = weights[a];
+    const float w = weights ? weights[a] : 1.f;
     const uint4 raw = *reinterpret_cast<const uint4*>(x + (int64_t)(a / top) * K + c * 8);
     const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t out[4];
@@ -1046,7 +1113,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
         for (int half = 0; half < 2; ++half) {
             const int m = wm * TM + i * 16 + (lane >> 2) + half * 8;
             if (m >= rows) continue;
-            const int64_t out_row = UP ? (int64_t)(row0 + m) : (int64_t)perm[row0 + m];
+            const bool squared = !UP && hidden != nullptr;  // an expert without a gate branch: relu(z)^2 into the hidden rows
+            const int64_t out_row = (UP || squared) ? (int64_t)(row0 + m) : (int64_t)perm[row0 + m];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const int n = n0 + wn * TN + j * 8 + ((lane & 3) << 1);
@@ -1055,6 +1123,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
                     const float h0 = silu_mul<true>(acc[0][i][j][half * 2], acc[U - 1][i][j][half * 2]);
                     const float h1 = silu_mul<true>(acc[0][i][j][half * 2 + 1], acc[U - 1][i][j][half * 2 + 1]);
                     *reinterpret_cast<__nv_bfloat162*>(hidden + out_row * n_out + n) = __floats2bfloat162_rn(h0, h1);
+                } else if (squared) {
+                    *reinterpret_cast<__nv_bfloat162*>(hidden + out_row * n_out + n) =
+                        __floats2bfloat162_rn(relu_square(acc[0][i][j][half * 2]), relu_square(acc[0][i][j][half * 2 + 1]));
                 } else {
                     *reinterpret_cast<float2*>(y + out_row * n_out + n) = make_float2(acc[0][i][j][half * 2], acc[0][i][j][half * 2 + 1]);
                 }
@@ -1394,15 +1465,18 @@ extern "C" int ss_turn_heads(void* x, const int32_t* positions, const float* inv
     return SS_LAUNCH_CHECK();
 }
 
-// ---------------------------------------------------------------- soft cap:  x <- cap * tanh(x / cap)
-__global__ void soft_cap_kernel(float* __restrict__ x, int64_t n, float cap) {
+// ---------------------------------------------------------------- soft cap:  x <- cap * tanh(scale * x / cap)
+// (cap 0: x <- scale * x)
+__global__ void soft_cap_kernel(float* __restrict__ x, int64_t n, float cap, float scale) {
     pdl_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+    if (i >= n) return;
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
 }
 
-extern "C" int ss_soft_cap(float* x, int64_t n, float cap, cudaStream_t stream) {
+extern "C" int ss_soft_cap(float* x, int64_t n, float cap, cudaStream_t stream, float scale) {
     if (n <= 0) return 0;
-    ss_launch(soft_cap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+    ss_launch(soft_cap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap, scale);
     return SS_LAUNCH_CHECK();
 }

@@ -16,7 +16,8 @@
 // ---------------------------------------------------------------- hyper-connections
 //
 // A token has S streams x_0 .. x_{S-1} of `hidden` floats (streams: [tokens][S][hidden]).  One launch does, per token,
-//   write:  x_t <- sum_s mix[s][t] x_s + w_out[t] * y          (all t from the old streams; skipped when y is null)
+//   write:  x_t <- sum_s mix[s][t] x_s + w_out[t] * y          (all t from the old streams; skipped when y is null;
+//           with y2, two branches that read the same input, y stands for y + y2, added in float32)
 //   read:   u = sum_t w_in[t] x_t
 //   norm:   out = u / sqrt(mean(u^2) + eps) * weight            (rounded once, to the output type)
 // With `rows`, output row i is token rows[i] and the streams stay as they are (the write is only applied on the way
@@ -26,7 +27,8 @@
 #define HC_MAX_STREAMS 8
 
 template <typename T, int SMAX>
-__global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
+__global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, const T* __restrict__ y2,
+                               const float* __restrict__ mix,
                                const float* __restrict__ w_out, const float* __restrict__ w_in,
                                const void* __restrict__ weight, int w_f32, T* __restrict__ out,
                                const int32_t* __restrict__ rows, int S, int hidden, float eps) {
@@ -44,6 +46,7 @@ __global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict_
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* base = streams + src * (int64_t)S * hidden;
     const T* yr = y ? y + src * (int64_t)hidden : nullptr;
+    const T* y2r = (y && y2) ? y2 + src * (int64_t)hidden : nullptr;  // a second output of the same branch point
     const bool write_back = rows == nullptr && y != nullptr;
 
     float ss = 0.f;
@@ -53,7 +56,7 @@ __global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict_
         for (int s = 0; s < SMAX; ++s) x[s] = s < S ? base[(int64_t)s * hidden + j] : 0.f;
         float u = 0.f;
         if (yr) {
-            const float yv = to_float(yr[j]);
+            const float yv = y2r ? to_float(yr[j]) + to_float(y2r[j]) : to_float(yr[j]);
 #pragma unroll
             for (int t = 0; t < SMAX; ++t) {
                 if (t >= S) break;
@@ -80,7 +83,7 @@ __global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict_
         for (int s = 0; s < SMAX; ++s) x[s] = s < S ? base[(int64_t)s * hidden + j] : 0.f;
         float u = 0.f;
         if (yr && !write_back) {
-            const float yv = to_float(yr[j]);
+            const float yv = y2r ? to_float(yr[j]) + to_float(y2r[j]) : to_float(yr[j]);
 #pragma unroll
             for (int t = 0; t < SMAX; ++t) {
                 if (t >= S) break;
@@ -123,7 +126,8 @@ __device__ __forceinline__ void st4(bf16* p, const float (&v)[4]) {
 // arithmetic behind every value is the kernel's above, operation for operation.
 #define HC_NV 4
 template <typename T, int SMAX>
-__global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
+__global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restrict__ y, const T* __restrict__ y2,
+                                   const float* __restrict__ mix,
                                    const float* __restrict__ w_out, const float* __restrict__ w_in,
                                    const void* __restrict__ weight, int w_f32, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int S, int hidden, float eps) {
@@ -140,6 +144,7 @@ __global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restr
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* base = streams + src * (int64_t)S * hidden;
     const T* yr = y ? y + src * (int64_t)hidden : nullptr;
+    const T* y2r = (y && y2) ? y2 + src * (int64_t)hidden : nullptr;  // a second output of the same branch point
     const bool write_back = rows == nullptr && y != nullptr;
     float u[HC_NV][4];
     float ss = 0.f;
@@ -155,6 +160,12 @@ __global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restr
         if (yr) {
             float yv[4];
             ld4(yr + j, yv);
+            if (y2r) {
+                float y2v[4];
+                ld4(y2r + j, y2v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) yv[e] += y2v[e];
+            }
 #pragma unroll
             for (int t = 0; t < SMAX; ++t) {
                 if (t >= S) break;
@@ -199,14 +210,14 @@ __global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restr
 }
 
 template <typename T>
-static int launch_hc_norm(float* streams, const void* y, const float* mix, const float* w_out, const float* w_in,
+static int launch_hc_norm(float* streams, const void* y, const void* y2, const float* mix, const float* w_out, const float* w_in,
                           const void* weight, int w_f32, void* out, const int32_t* rows, int n_rows, int S, int hidden,
                           float eps, cudaStream_t stream) {
     if (hidden % 4 == 0 && hidden <= 16 * 512 && S <= 4) {
         int vthreads = ((hidden / 4 + HC_NV - 1) / HC_NV + 31) / 32 * 32;
         vthreads = vthreads < 64 ? 64 : vthreads;
 #define HC_VEC(SMAX)                                                                                                     \
-    ss_launch(hc_norm_vec_kernel<T, SMAX>, dim3(n_rows), dim3(vthreads), 0, stream, streams, (const T*)y, mix, w_out, w_in, \
+    ss_launch(hc_norm_vec_kernel<T, SMAX>, dim3(n_rows), dim3(vthreads), 0, stream, streams, (const T*)y, (const T*)y2, mix, w_out, w_in, \
               weight, w_f32, (T*)out, rows, S, hidden, eps)
         if (S == 1) HC_VEC(1);
         else if (S == 2) HC_VEC(2);
@@ -216,7 +227,7 @@ static int launch_hc_norm(float* streams, const void* y, const float* mix, const
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
 #define HC_GO(SMAX)                                                                                                   \
-    ss_launch(hc_norm_kernel<T, SMAX>, dim3(n_rows), dim3(threads), 0, stream, streams, (const T*)y, mix, w_out, w_in, \
+    ss_launch(hc_norm_kernel<T, SMAX>, dim3(n_rows), dim3(threads), 0, stream, streams, (const T*)y, (const T*)y2, mix, w_out, w_in, \
               weight, w_f32, (T*)out, rows, S, hidden, eps)
     if (S == 1) HC_GO(1);
     else if (S == 2) HC_GO(2);
@@ -230,12 +241,12 @@ static int launch_hc_norm(float* streams, const void* y, const float* mix, const
 // ones) float32 on the device; weight [hidden] in the output type or float32; rows: int32 [n_rows] or null.
 extern "C" int ss_hc_norm(float* streams, const void* y, const float* mix, const float* w_out, const float* w_in,
                           const void* weight, int w_f32, void* out, const int32_t* rows, int n_rows, int S, int hidden,
-                          float eps, int dtype, cudaStream_t stream) {
+                          float eps, int dtype, cudaStream_t stream, const void* y2) {
     if (n_rows <= 0) return 0;
     if (S < 1 || S > HC_MAX_STREAMS || (y != nullptr && (!mix || !w_out))) return (int)cudaErrorInvalidValue;
     if (dtype == SS_BF16)
-        return launch_hc_norm<bf16>(streams, y, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
-    return launch_hc_norm<float>(streams, y, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
+        return launch_hc_norm<bf16>(streams, y, y2, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
+    return launch_hc_norm<float>(streams, y, y2, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
 }
 
 // ---------------------------------------------------------------- rotation, unit norm, page write

@@ -54,7 +54,7 @@ _OPS_SIGNATURES = {
                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "ss_mark_seen": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ss_hc_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                   c_int, c_float, c_int, c_void_p],
+                   c_int, c_float, c_int, c_void_p, c_void_p],
     "ss_rope_norm_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
     "ss_glu_limited": [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
@@ -66,10 +66,11 @@ _OPS_SIGNATURES = {
                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_ssm_scan": [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
-    "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                  c_int, c_int, c_void_p, c_int],
+    "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                    c_int, c_int, c_int, c_int, c_int, c_void_p],
+                    c_int, c_int, c_int, c_int, c_int, c_void_p, c_int],
     "ss_moe_gemm_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -78,7 +79,7 @@ _OPS_SIGNATURES = {
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p,
                            c_void_p],
     "ss_turn_heads": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "ss_soft_cap": [c_void_p, c_int64, c_float, c_void_p],
+    "ss_soft_cap": [c_void_p, c_int64, c_float, c_void_p, c_float],
     "ss_embed_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ss_matrix_cell": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
@@ -91,6 +92,17 @@ _OPS_SIGNATURES = {
     "ss_xielu": [c_void_p, c_void_p, c_int64, c_float, c_float, c_int, c_void_p],
     "ss_latent_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_void_p],
+    "ss_decay_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_gated_rmsnorm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "ss_block_gates": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_gated_linear_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_head_gate": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_scaled_sum": [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int64, c_int, c_void_p],
+    "ss_relu_square": [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ss_moe_mix": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                   c_int, c_int, c_int, c_int, c_void_p],
     "ss_head_product": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_void_p],
 }
@@ -156,7 +168,7 @@ def ops_library() -> ctypes.CDLL:
     lib = _state.get("ops")
     if lib is None:
         require_cuda()
-        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "ops_mixers.cu", "ops_cells.cu", "sampling.cu"])
+        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "ops_mixers.cu", "ops_cells.cu", "ops_gated.cu", "sampling.cu"])
         _declare(lib, _OPS_SIGNATURES)
         _state["ops"] = lib
     return lib  # type: ignore[return-value]
@@ -349,12 +361,13 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
 
 def hc_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | None, w_out: torch.Tensor | None,
             w_in: torch.Tensor | None, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
-            rows: torch.Tensor | None = None) -> torch.Tensor:
+            rows: torch.Tensor | None = None, y2: torch.Tensor | None = None) -> torch.Tensor:
     """One hyper-connection step on ``streams`` (float32 [N, S, H], changed in place).  Write: stream t becomes
     ``sum_s mix[s, t] * stream s + w_out[t] * y`` (skipped when ``y`` is None).  Read: ``u = sum_t w_in[t] * stream t``
     (``w_in`` None: the plain sum).  Norm: returns ``u / sqrt(mean(u^2) + eps) * weight`` in ``out_dtype`` [N, H],
     all in float32 with one rounding at the end.  ``mix`` [S, S], ``w_out`` [S], ``w_in`` [S]: float32 on the device.
-    With ``rows`` (int32 [M]) only those tokens are produced and the streams are left as they are."""
+    With ``rows`` (int32 [M]) only those tokens are produced and the streams are left as they are.  ``y2``: a second
+    output of the same branch point (two branches that read one input); ``y + y2``, added in float32, is written."""
     _need(streams, torch.float32, "streams")
     if streams.dim() != 3:
         raise KernelError("streams must be [tokens, streams, hidden]")
@@ -367,6 +380,12 @@ def hc_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | N
         _need(w_out, torch.float32, "w_out")
         if mix.numel() != s * s or w_out.numel() != s:
             raise KernelError("mix must be [S, S] and w_out [S]")
+        if y2 is not None:
+            _need(y2, out_dtype, "second branch output")
+            if y2.shape != y.shape:
+                raise KernelError("the two branch outputs differ in shape")
+    elif y2 is not None:
+        raise KernelError("a second branch output comes with a first")
     if w_in is not None:
         _need(w_in, torch.float32, "w_in")
         if w_in.numel() != s:
@@ -382,7 +401,7 @@ def hc_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | N
     _check(ops_library().ss_hc_norm(streams.data_ptr(), _ptr(y), _ptr(mix) if y is not None else None,
                                     _ptr(w_out) if y is not None else None, _ptr(w_in), weight.data_ptr(), w_f32,
                                     out.data_ptr(), _ptr(rows), n_out, s, hidden, float(eps), _code(out_dtype),
-                                    _stream()), "hc_norm")
+                                    _stream(), _ptr(y2)), "hc_norm")
     return out
 
 
@@ -1471,13 +1490,16 @@ def round_stream(residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor
 
 
 def conv_silu(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, bias: torch.Tensor | None,
-              state: torch.Tensor, ctx, plus_input: bool = False) -> torch.Tensor:
+              state: torch.Tensor, ctx, plus_input: bool = False, activation: bool = True) -> torch.Tensor:
     """``silu`` of a causal convolution per channel over each request's tokens.  Channel c of a token is
     ``proj[row, col0 + c]``; ``taps`` float32 [channels, T] (the last column multiplies the current token);
     ``state`` float32 [slots, T - 1, channels] holds each request's last T - 1 inputs (zeros for a request that
     starts), is read for the tokens in front of the step and left holding the step's last inputs.  Returns
     [N, channels] in the dtype of ``proj``.  ``plus_input``: the result is ``input + convolution`` with no activation
-    instead (a convolution laid over a branch's input)."""
+    instead (a convolution laid over a branch's input).  ``activation`` False: the convolution (with its bias) as it
+    is."""
+    if plus_input and not activation:
+        raise KernelError("conv_silu: plus_input has no activation already")
     _need(proj, None, "projection")
     _need(taps, torch.float32, "taps")
     _need(state, torch.float32, "convolution state")
@@ -1494,7 +1516,7 @@ def conv_silu(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, 
                                       state.data_ptr(), out.data_ptr(), ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(),
                                       ctx.state_slots.data_ptr(), ctx.num_requests, n, channels, n_taps, state.shape[0],
                                       int(ctx.is_decode_only), _code(proj.dtype), error_word(proj.device).data_ptr(),
-                                      _stream(), int(plus_input)), "conv_silu")
+                                      _stream(), 1 if plus_input else (0 if activation else 2)), "conv_silu")
     if not ctx.is_decode_only and n_taps > 1:
         _launches[0] += 1  # the state's update is a launch of its own
     return out
@@ -1525,21 +1547,36 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
     return y
 
 
-def router(x: torch.Tensor, weight: torch.Tensor, top: int, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
-    """Sigmoid router: logits ``x @ weight.T`` in float32, the ``top`` largest per token chosen (the lower index on a
-    tie).  Returns (int32 [N, top] experts, float32 [N, top] their scores ``sigmoid(logit)``, divided by their sum with
-    ``renormalize``)."""
+def router(x: torch.Tensor, weight: torch.Tensor, top: int, renormalize: bool = False, *, softmax: bool = False,
+           correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1,
+           extra: int = 0) -> "tuple[torch.Tensor, torch.Tensor] | tuple[torch.Tensor, torch.Tensor, torch.Tensor]":
+    """Router: logits ``x @ weight.T`` in float32, scores their sigmoid (or, with ``softmax``, their softmax over all
+    experts), the ``top`` largest per token chosen (the lower index on a tie).  ``correction`` (float32 [experts]) is
+    added to the scores for the choice only.  ``groups`` > 1: the experts form that many equal groups of neighbours, a
+    group's score is its largest choice score, and only experts of the ``keep`` best groups can be chosen.  Returns
+    (int32 [N, top] experts, float32 [N, top] their scores without the correction, divided by their sum with
+    ``renormalize``).  ``extra``: the last ``extra`` rows of ``weight`` are not experts; their logits ride along in the
+    product and come back as a third result, float32 [N, extra]."""
     _need(x, None, "x")
     _need(weight, x.dtype, "router weight")
     n, hidden = x.shape
-    experts = weight.shape[0]
-    if weight.shape[1] != hidden or not 1 <= top <= experts or experts > 1024 or (hidden + experts) * 4 > 48 * 1024:
+    experts = weight.shape[0] - int(extra)
+    if (weight.shape[1] != hidden or not 1 <= top <= experts or experts > 1024 or extra < 0
+            or (hidden + 2 * experts + groups) * 4 > 48 * 1024):
         raise KernelError("router: sizes out of range")
+    if groups < 1 or experts % groups or not 1 <= keep <= groups or top > keep * (experts // groups):
+        raise KernelError("router: the experts do not split into such groups, or too few are kept for the choices")
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        if correction.numel() != experts:
+            raise KernelError("router: one correction per expert")
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    rest = torch.empty((n, extra), dtype=torch.float32, device=x.device) if extra else None
     _check(ops_library().ss_router(x.data_ptr(), weight.data_ptr(), ids.data_ptr(), scores.data_ptr(), n, hidden, experts,
-                                   int(top), int(renormalize), _code(x.dtype), _stream()), "router")
-    return ids, scores
+                                   int(top), int(renormalize), _code(x.dtype), _stream(), int(softmax), _ptr(correction),
+                                   int(groups), int(keep), _ptr(rest), int(extra)), "router")
+    return (ids, scores, rest) if extra else (ids, scores)
 
 
 MOE_TILE = 64  # rows of one expert that a block of the grouped products takes
@@ -1583,7 +1620,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_u
     tile_row0, tile_rows = plan[2 * a + max_tiles: 2 * a + 2 * max_tiles], plan[2 * a + 2 * max_tiles:]
     lib = ops_library()
     _check(lib.ss_moe_plan(ids.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
-                           tile_rows.data_ptr(), a, experts, tile, max_tiles, place.data_ptr(), _stream()), "moe_plan")
+                           tile_rows.data_ptr(), a, experts, tile, max_tiles, place.data_ptr(), _stream(), experts), "moe_plan")
     hidden_act = torch.empty((a, ff), dtype=x.dtype, device=x.device)
     lists = (perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr())
     if tensor_cores:
@@ -1608,9 +1645,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_u
                                    max_tiles, tile, 0, 0, int(a <= 4), _stream()), "moe_down")
         return y, None
     _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, top,
-                           hidden, ff, max_tiles, 1, _code(x.dtype), run, _stream()), "moe_up")
+                           hidden, ff, max_tiles, 1, _code(x.dtype), run, _stream(), 0), "moe_up")
     _check(lib.ss_moe_gemm(hidden_act.data_ptr(), None, down.data_ptr(), *lists, None, y.data_ptr(), top, ff, hidden,
-                           max_tiles, 0, _code(x.dtype), 0, _stream()), "moe_down")
+                           max_tiles, 0, _code(x.dtype), 0, _stream(), 0), "moe_down")
     return y, None
 
 
@@ -1694,10 +1731,10 @@ def turn_heads(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                                        int(dims), int(interleaved), float(sign), _code(x.dtype), _stream()), "turn_heads")
 
 
-def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
-    """``x <- cap * tanh(x / cap)`` in place (float32)."""
+def soft_cap(x: torch.Tensor, cap: float | None, scale: float = 1.0) -> torch.Tensor:
+    """``x <- cap * tanh(scale * x / cap)`` in place (float32); without a cap ``x <- scale * x``."""
     _need(x, torch.float32, "x")
-    _check(ops_library().ss_soft_cap(x.data_ptr(), x.numel(), float(cap), _stream()), "soft_cap")
+    _check(ops_library().ss_soft_cap(x.data_ptr(), x.numel(), float(cap or 0.0), _stream(), float(scale)), "soft_cap")
     return x
 
 
@@ -1907,6 +1944,228 @@ def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.
 
 
 
+# --------------------------------------------------------------------------- decayed linear attention, gated linear recurrence
+
+def decay_attention(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx, heads: int, dim: int,
+                    value_dim: int) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over each request's tokens, continued from and left in ``state``
+    (float32 [slots, heads, value_dim, dim]).  A row of ``proj`` starts with the heads' queries, then keys (``dim``
+    each), then values (``value_dim``), all before their activation; whatever follows is left alone.  Per head h, token
+    by token: ``S <- decay[h] S + silu(k) silu(v)^T``, ``o = S^T silu(q)``.  Returns o float32 [N, heads * value_dim]."""
+    _need(proj, None, "projected rows")
+    _need(decay, torch.float32, "decay")
+    _need(state, torch.float32, "state")
+    n = proj.shape[0]
+    if proj.shape[1] < heads * (2 * dim + value_dim) or decay.numel() != heads or not 1 <= dim <= 256:
+        raise KernelError("decay_attention: the rows are narrower than their heads, or sizes out of range")
+    if tuple(state.shape[1:]) != (heads, value_dim, dim):
+        raise KernelError("decay_attention: the state must be [slots, heads, value_dim, dim]")
+    out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=proj.device)
+    _check(ops_library().ss_decay_attention(proj.data_ptr(), proj.stride(0), decay.data_ptr(), state.data_ptr(),
+                                            out.data_ptr(), ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(),
+                                            ctx.state_slots.data_ptr(), ctx.num_requests, heads, dim, value_dim,
+                                            state.shape[0], _code(proj.dtype), error_word(proj.device).data_ptr(), _stream()),
+           "decay_attention")
+    return out
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate)`` row by row: ``x`` float32 [N, C], ``gate`` a view [N, C] in
+    ``out_dtype`` with unit inner stride, ``weight`` float32 [C]; float32 arithmetic, one rounding."""
+    _need(x, torch.float32, "x")
+    _need(weight, torch.float32, "norm weight")
+    n, c = x.shape
+    if gate.dtype != out_dtype or tuple(gate.shape) != (n, c) or gate.stride(1) != 1 or weight.numel() != c:
+        raise KernelError("gated_rmsnorm: the gate must be [N, C] in the compute dtype with unit inner stride, the weight [C]")
+    out = torch.empty((n, c), dtype=out_dtype, device=x.device)
+    _check(ops_library().ss_gated_rmsnorm(x.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(),
+                                          n, c, float(eps), _code(out_dtype), _stream()), "gated_rmsnorm")
+    return out
+
+
+BLOCK_GATES_LIBRARY_ROWS = 128  # rows from which the gates' block products go to the library's batched product
+
+
+def block_gates(u: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Two gates' pre-activations from square blocks of the input: ``u`` [N, blocks * bs]; ``weight`` [blocks, 2 bs, bs]
+    (per block the first gate's rows, then the second's).  Returns float32 [blocks, N, 2 bs]:
+    ``pre[b, t] = weight[b] @ u[t, b bs : (b + 1) bs]``, accumulated in float32.  Many bfloat16 rows run the library's
+    batched product with a float32 result (its inputs are the same bfloat16 numbers, its sums float32)."""
+    _need(u, None, "u")
+    _need(weight, u.dtype, "gate weights")
+    n = u.shape[0]
+    blocks, two_bs, bs = weight.shape
+    if two_bs != 2 * bs or u.shape[1] != blocks * bs:
+        raise KernelError("block_gates: weight must be [blocks, 2 bs, bs] and u [N, blocks * bs]")
+    if u.dtype == torch.bfloat16 and n >= BLOCK_GATES_LIBRARY_ROWS and bs % 8 == 0:
+        return torch.bmm(u.view(n, blocks, bs).transpose(0, 1), weight.transpose(1, 2), out_dtype=torch.float32)
+    pre = torch.empty((blocks, n, two_bs), dtype=torch.float32, device=u.device)
+    _check(ops_library().ss_block_gates(u.data_ptr(), u.stride(0), weight.data_ptr(), None, pre.data_ptr(), n, blocks, bs,
+                                        _code(u.dtype), _stream()), "block_gates")
+    return pre
+
+
+def gated_linear_recurrence(pre: torch.Tensor, bias: torch.Tensor | None, u: torch.Tensor, y: torch.Tensor, lam: torch.Tensor,
+                            rate: float, state: torch.Tensor, ctx) -> torch.Tensor:
+    """The real-gated linear recurrence over each request's tokens, continued from and left in ``state`` (float32
+    [slots, C]).  ``pre`` float32 [blocks, N, 2 bs] (`block_gates`), ``bias`` float32 [blocks, 2 bs] or None, ``u``
+    [N, C] the recurrence's input, ``y`` a view [N, C] (unit inner stride) of the other branch before its activation,
+    ``lam`` float32 [C].  Per channel: ``r = sigmoid(pre1 + bias1)``, ``i = sigmoid(pre2 + bias2)``,
+    ``a = exp(-rate r softplus(lam))``, ``S <- a S + sqrt(1 - a^2) i u``; returns ``S gelu_tanh(y)`` [N, C] in the
+    dtype of ``u``."""
+    _need(pre, torch.float32, "gate pre-activations")
+    _need(u, None, "u")
+    _need(lam, torch.float32, "lam")
+    _need(state, torch.float32, "state")
+    blocks, n, two_bs = pre.shape
+    bs, c = two_bs // 2, u.shape[1]
+    if u.shape[0] != n or blocks * bs != c or lam.numel() != c or tuple(state.shape[1:]) != (c,):
+        raise KernelError("gated_linear_recurrence: shapes do not match")
+    if y.dtype != u.dtype or tuple(y.shape) != (n, c) or y.stride(1) != 1:
+        raise KernelError("gated_linear_recurrence: y must be a view [N, C] with unit inner stride in the dtype of u")
+    if bias is not None:
+        _need(bias, torch.float32, "gate biases")
+        if bias.numel() != blocks * two_bs:
+            raise KernelError("gated_linear_recurrence: one bias per gate and channel")
+    out = torch.empty((n, c), dtype=u.dtype, device=u.device)
+    _check(ops_library().ss_gated_linear_recurrence(pre.data_ptr(), _ptr(bias), u.data_ptr(), y.data_ptr(), y.stride(0),
+                                                    lam.data_ptr(), float(rate), state.data_ptr(), out.data_ptr(),
+                                                    ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
+                                                    ctx.num_requests, n, c, bs, state.shape[0], _code(u.dtype),
+                                                    error_word(u.device).data_ptr(), _stream()), "gated_linear_recurrence")
+    return out
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int) -> None:
+    """``x[t, h * D + d] *= sigmoid(gate[t, h])`` in place: ``x`` [N, heads * D] contiguous, ``gate`` a view [N, heads]
+    with unit inner stride in the same dtype."""
+    _need(x, None, "x")
+    n = x.shape[0]
+    if x.shape[1] != heads * head_dim or gate.dtype != x.dtype or tuple(gate.shape) != (n, heads) or gate.stride(1) != 1:
+        raise KernelError("head_gate: x must be [N, heads * D] and the gate a view [N, heads] of the same dtype")
+    _check(ops_library().ss_head_gate(x.data_ptr(), gate.data_ptr(), gate.stride(0), n, heads, head_dim, _code(x.dtype),
+                                      _stream()), "head_gate")
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float) -> torch.Tensor:
+    """``scale_a * a + scale_b * b`` element by element, formed in float32 and rounded once."""
+    _need(a, None, "a")
+    _need(b, a.dtype, "b")
+    if a.shape != b.shape:
+        raise KernelError("scaled_sum: shapes differ")
+    out = torch.empty_like(a)
+    _check(ops_library().ss_scaled_sum(a.data_ptr(), float(scale_a), b.data_ptr(), float(scale_b), out.data_ptr(), a.numel(),
+                                       _code(a.dtype), _stream()), "scaled_sum")
+    return out
+
+
+def relu_square(x: torch.Tensor, cols: int | None = None) -> torch.Tensor:
+    """``relu(x)^2`` of the first ``cols`` columns (default: all) of ``x`` [N, width] as a new contiguous [N, cols]."""
+    if x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda:
+        raise KernelError("relu_square takes a CUDA tensor [N, width] with unit inner stride")
+    cols = x.shape[1] if cols is None else int(cols)
+    out = torch.empty((x.shape[0], cols), dtype=x.dtype, device=x.device)
+    _check(ops_library().ss_relu_square(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], cols, _code(x.dtype),
+                                        _stream()), "relu_square")
+    return out
+
+
+def moe_experts_single(x: torch.Tensor, ids: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                       slots: int | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """The chosen experts of every token for experts without a gate branch: ``y[t, k] = W_down[e] relu(W_up[e] x[t])^2``
+    with ``e = ids[t, k]``; no weight is applied here (`moe_mix` weighs the outputs).  ``up`` [experts, ff, hidden],
+    ``down`` [experts, hidden, ff].  ``slots`` (default: experts): ids from ``experts`` up to ``slots`` name experts
+    without weights; their terms are not computed (and must not be read).  Returns what `moe_experts` returns, by the
+    same three routes (CUDA cores; mma.sync tiles; the grouped two-SM tcgen05 kernel with the activation behind it)."""
+    n, hidden = x.shape
+    experts, ff, _ = up.shape
+    top = ids.shape[1]
+    slots = experts if slots is None else int(slots)
+    _need(x, None, "x")
+    _need(up, x.dtype, "up")
+    _need(down, x.dtype, "down")
+    _need(ids, torch.int32, "ids")
+    if tuple(down.shape) != (experts, hidden, ff) or up.shape[2] != hidden or slots < experts or slots > 1024:
+        raise KernelError("moe_experts_single: weights of the wrong shape")
+    a = n * top
+    tensor_cores = x.dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0
+    tcgen05 = tensor_cores and hidden % 16 == 0 and ff % 16 == 0 and a >= GROUPED_TCGEN05_ROWS
+    tile = MOE_TILE if not tensor_cores else (256 if tcgen05 else (128 if a >= 96 * experts else 32))
+    max_tiles = (a + tile - 1) // tile + slots
+    plan = torch.empty(2 * a + 3 * max_tiles, dtype=torch.int32, device=x.device)
+    perm, place, tile_expert = plan[:a], plan[a: 2 * a], plan[2 * a: 2 * a + max_tiles]
+    tile_row0, tile_rows = plan[2 * a + max_tiles: 2 * a + 2 * max_tiles], plan[2 * a + 2 * max_tiles:]
+    lib = ops_library()
+    _check(lib.ss_moe_plan(ids.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
+                           tile_rows.data_ptr(), a, slots, tile, max_tiles, place.data_ptr(), _stream(), experts), "moe_plan")
+    hidden_act = torch.empty((a, ff), dtype=x.dtype, device=x.device)
+    lists = (perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr())
+    if tensor_cores:
+        gathered = torch.empty((a, hidden), dtype=x.dtype, device=x.device)
+        _check(lib.ss_moe_gather(x.data_ptr(), None, perm.data_ptr(), gathered.data_ptr(), a, top, hidden, _stream()),
+               "moe_gather")
+    if tcgen05:
+        err = error_word(x.device).data_ptr()
+        y_sorted = torch.empty((a, hidden), dtype=x.dtype, device=x.device)
+        _check(gemm_library().ss_gemm_tc5_grouped(gathered.data_ptr(), up.data_ptr(), hidden_act.data_ptr(), a, ff, hidden,
+                                                  experts, ff, ff, 0, *lists[1:], max_tiles, err, _stream()), "moe_up")
+        _check(lib.ss_relu_square(hidden_act.data_ptr(), ff, hidden_act.data_ptr(), a, ff, _code(x.dtype), _stream()),
+               "relu_square")
+        _check(gemm_library().ss_gemm_tc5_grouped(hidden_act.data_ptr(), down.data_ptr(), y_sorted.data_ptr(), a, hidden, ff,
+                                                  experts, hidden, hidden, 0, *lists[1:], max_tiles, err, _stream()),
+               "moe_down")
+        return y_sorted, place
+    y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
+    if tensor_cores:
+        _check(lib.ss_moe_gemm_mma(gathered.data_ptr(), up.data_ptr(), *lists, hidden_act.data_ptr(), None, hidden, ff,
+                                   max_tiles, tile, 0, 0, int(a <= 4), _stream()), "moe_up")
+        _check(lib.ss_moe_gemm_mma(hidden_act.data_ptr(), down.data_ptr(), *lists, None, y.data_ptr(), ff, hidden,
+                                   max_tiles, tile, 0, 0, int(a <= 4), _stream()), "moe_down")
+        return y, None
+    _check(lib.ss_moe_gemm(x.data_ptr(), None, up.data_ptr(), *lists, hidden_act.data_ptr(), None, top, hidden, ff,
+                           max_tiles, 0, _code(x.dtype), 0, _stream(), 1), "moe_up")
+    _check(lib.ss_moe_gemm(hidden_act.data_ptr(), None, down.data_ptr(), *lists, None, y.data_ptr(), top, ff, hidden,
+                           max_tiles, 0, _code(x.dtype), 0, _stream(), 0), "moe_down")
+    return y, None
+
+
+def moe_mix(y: torch.Tensor, term_rows: torch.Tensor | None, ids: torch.Tensor, weights: torch.Tensor | None, experts: int,
+            x: torch.Tensor, shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
+    """``sum_k weights[t, k] * term(t, k) + sigmoid(shared_gate[t]) * shared[t]`` in float32, in the order of the
+    choices, rounded once to the dtype of ``x``.  ``term(t, k)`` is expert ``ids[t, k]``'s output in either form that
+    `moe_experts` returns, or, for an id from ``experts`` on (an expert that hands its input on), ``x[t]``.
+    ``weights`` None: ones; ``shared_gate`` (float32, one logit per token, any stride) None: the shared expert's
+    output as it is."""
+    _need(x, None, "x")
+    _need(ids, torch.int32, "ids")
+    n, hidden = x.shape
+    top = ids.shape[1]
+    if term_rows is None:
+        _need(y, torch.float32, "expert outputs")
+        if tuple(y.shape) != (n, top, hidden):
+            raise KernelError("moe_mix: the experts' outputs must be [N, top, hidden]")
+    else:
+        _need(y, torch.bfloat16, "sorted expert outputs")
+        _need(term_rows, torch.int32, "term_rows")
+        if x.dtype != torch.bfloat16 or y.shape[1] != hidden or term_rows.numel() != n * top:
+            raise KernelError("moe_mix: sorted rows come with bfloat16 inputs and one place per choice")
+    if weights is not None:
+        _need(weights, torch.float32, "weights")
+    if shared is not None:
+        _need(shared, x.dtype, "shared expert output")
+    gate_stride = 0
+    if shared_gate is not None:
+        if shared is None or shared_gate.dtype != torch.float32 or shared_gate.shape[0] != n:
+            raise KernelError("moe_mix: the shared expert's gate is one float32 logit per token")
+        gate_stride = shared_gate.stride(0)
+    out = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
+    _check(ops_library().ss_moe_mix(y.data_ptr() if term_rows is None else None, _ptr(y) if term_rows is not None else None,
+                                    _ptr(term_rows), ids.data_ptr(), _ptr(weights), int(experts), x.data_ptr(), _ptr(shared),
+                                    _ptr(shared_gate), gate_stride, out.data_ptr(), n, hidden, top, _code(x.dtype), _stream()),
+           "moe_mix")
+    return out
+
+
 def set_programmatic_launch(enabled: bool) -> None:
     """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
     libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if isinstance(key, str) and key.startswith("attn")]
@@ -1921,4 +2180,5 @@ __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_no
            "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "tcgen05_prefill_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library", "group_norm", "round_stream", "conv_silu", "ssm_scan", "router", "moe_experts", "moe_combine",
            "norm_rope_cache", "turn_heads", "soft_cap", "embed_sum", "matrix_cell", "cell_output", "gated_recurrence", "xielu",
-           "latent_rows", "head_product"]
+           "latent_rows", "head_product", "decay_attention", "gated_rmsnorm", "block_gates", "gated_linear_recurrence", "head_gate",
+           "scaled_sum", "relu_square", "moe_experts_single", "moe_mix"]

@@ -4,13 +4,14 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    Embedding, FeedForward, Head, IntoNorm, LayerBinding, Mixer, Norm, Part, PositionEncoding, Registry, Runtime,
                    StateSpec, WeightSpec)
 from .attention import PagedAttention
-from .block import BranchNormBlock, PreNormBlock
+from .block import BranchNormBlock, ParallelBlock, PreNormBlock
 from .embedding import LMHead, SummedEmbedding, TokenEmbedding
 from .mlp import ActivatedFeedForward, GatedFeedForward, SwiGLUFeedForward
 from .experts import RoutedExperts
 from .norm import GroupRMSNorm, RMSNorm, StreamRounding
 from .state_space import StateSpaceMixer
-from .recurrent import ConvolvedInput, GatedRecurrenceMixer, MatrixMemoryMixer
+from .recurrent import (ConvolvedInput, DecayedLinearAttention, GatedLinearRecurrenceMixer, GatedRecurrenceMixer,
+                        MatrixMemoryMixer, ParallelMixers)
 from .latent_attention import LatentAttention
 from .rotary import NoPositionEncoding, RotaryEncoding, YarnRotaryEncoding
 from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
@@ -21,4 +22,5 @@ __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS"
            "TokenEmbedding", "SwiGLUFeedForward", "GatedFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
            "HyperConnectionBlock", "StreamWrite", "BranchNormBlock", "GroupRMSNorm", "StreamRounding", "RoutedExperts",
            "StateSpaceMixer", "SummedEmbedding", "ActivatedFeedForward", "ConvolvedInput", "GatedRecurrenceMixer",
-           "MatrixMemoryMixer", "LatentAttention"]
+           "MatrixMemoryMixer", "LatentAttention", "ParallelBlock", "DecayedLinearAttention", "GatedLinearRecurrenceMixer",
+           "ParallelMixers"]

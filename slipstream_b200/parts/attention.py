@@ -20,7 +20,9 @@ elements with a weight of the head's size that all heads share (tensors ``q_norm
 the value of position j is rotated by j over all its elements, with the pairing of the position encoding and the
 frequencies ``theta^(-2m / value_dim)``, and cached so; a head's output at position i (the weighted sum of such
 values) is turned back by -i before any gate, so that what is summed depends on i - j only.  ``softcap`` c: a scaled
-score s enters the softmax as ``c tanh(s / c)``.  ``names``: the checkpoint's tensor names by role (q, k, v, o, g,
+score s enters the softmax as ``c tanh(s / c)``.  ``head_gate``: head h's output is multiplied by
+``sigmoid(w_g,h . x)``, one number per head and token (``W_g`` [heads, hidden] rides in the stacked product).
+``unit_sink``: the softmax's denominator holds one more 1 (a key whose score is 0 and which has no value).  ``names``: the checkpoint's tensor names by role (q, k, v, o, g,
 q_bias, k_bias, v_bias, o_bias, q_norm, k_norm).
 
 Heads of a size the kernels do not take (they take multiples of 16), or values of another size than keys, are
@@ -48,7 +50,8 @@ class PagedAttention(Mixer):
                  window: int | None = None, scale: float | None = None, page_size: int | None = None, *,
                  chunk: int | None = None, value_dim: int | None = None, unit_norm_eps: float | None = None,
                  gate: bool = False, has_kv: bool = True, names: dict[str, str] | None = None,
-                 qk_norm_eps: float | None = None, rotate_values: bool = False, softcap: float | None = None) -> None:
+                 qk_norm_eps: float | None = None, rotate_values: bool = False, softcap: float | None = None,
+                 head_gate: bool = False, unit_sink: bool = False) -> None:
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
         value_dim = head_dim if value_dim is None else int(value_dim)
@@ -80,8 +83,11 @@ class PagedAttention(Mixer):
         self.softcap = float(softcap) if softcap else None
         if self.rotate_values and (value_dim % 2 or getattr(position_encoding, "theta", None) is None):
             raise ValueError("rotated values need an even value size and a rotary position encoding")
-        if self.rotate_values and gate:
+        if self.rotate_values and (gate or head_gate):
             raise ValueError("a gate on rotated values is not built")
+        if gate and head_gate:
+            raise ValueError("a layer gates its heads element by element or head by head, not both")
+        self.head_gate, self.unit_sink = bool(head_gate), bool(unit_sink)
         if self.qk_norm_eps is not None and unit_norm_eps is not None:
             raise ValueError("a layer norms its heads before the rotation or after it, not both")
         self.has_kv = bool(has_kv)
@@ -100,6 +106,7 @@ class PagedAttention(Mixer):
         rotation (half-split pairs, unscaled sines, no unit norm, no gate, keys and values of its own)."""
         rotary_plain = getattr(self.position_encoding, "plain", True)
         return (rotary_plain and self.unit_norm_eps is None and not self.gate and self.has_kv
+                and not self.head_gate and not self.unit_sink
                 and self.qk_norm_eps is None and not self.rotate_values and self.softcap is None
                 and self.key_dim == self.value_dim == self.head_dim)
 
@@ -110,6 +117,8 @@ class PagedAttention(Mixer):
             specs += [WeightSpec(names["k"], (self.num_kv_heads * d, h)), WeightSpec(names["v"], (self.num_kv_heads * dv, h))]
         if self.gate:
             specs.append(WeightSpec(names["g"], (self.num_heads * dv, h)))
+        if self.head_gate:
+            specs.append(WeightSpec(names["g"], (self.num_heads, h)))
         if self.qkv_bias:
             specs.append(WeightSpec(names["q_bias"], (self.num_heads * d,), kind="vector"))
             if self.has_kv:
@@ -143,12 +152,20 @@ class PagedAttention(Mixer):
             roles += [("k", nkv, self.key_dim), ("v", nkv, self.value_dim)]
         if self.gate:
             roles.append(("g", nq, self.value_dim))
-        self.qkv_weight = torch.cat([self._pad_heads(weights[names[r]], heads, size) for r, heads, size in roles],
-                                    dim=0).contiguous()
+        stacked = [self._pad_heads(weights[names[r]], heads, size) for r, heads, size in roles]
+        self.head_gate_col = sum(t.shape[0] for t in stacked)
+        extra_rows = 0
+        if self.head_gate:  # one row per head behind the heads themselves, then zeros up to a row of 16-byte multiples
+            extra_rows = -(-nq // 8) * 8
+            g = weights[names["g"]]
+            stacked.append(torch.cat([g, g.new_zeros((extra_rows - nq, g.shape[1]))]))
+        self.qkv_weight = torch.cat(stacked, dim=0).contiguous()
         self.qkv_b = None
         if self.qkv_bias:
             biases = [self._pad_heads(weights[names[f"{r}_bias"]], heads, size) if r != "g"
                       else weights[names["q"]].new_zeros(heads * self.head_dim) for r, heads, size in roles]
+            if extra_rows:
+                biases.append(weights[names["q"]].new_zeros(extra_rows))
             self.qkv_b = torch.cat(biases).to(runtime.dtype).contiguous()
         o = weights[names["o"]]
         if self.value_dim != self.head_dim:
@@ -164,6 +181,7 @@ class PagedAttention(Mixer):
         if self.rotate_values:  # formed in double precision, rounded once
             pairs = torch.arange(0, self.value_dim, 2, dtype=torch.float64)
             self.value_inv_freq = (float(self.position_encoding.theta) ** (-pairs / self.value_dim)).to(torch.float32).to(runtime.device)
+        self.sinks = torch.zeros(nq, dtype=torch.float32, device=runtime.device) if self.unit_sink else None
         ops.attention_library(self.head_dim)  # compile now, not inside the first step
 
     # ------------------------------------------------------------------ decode steps replayed from a graph
@@ -252,7 +270,10 @@ class PagedAttention(Mixer):
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.scale, self.window or 0,
                             rope=(inv_freq, rotary_dim) if fused else None, chunk=self.chunk or 0,
-                            gate=qkv[:, qkv.shape[1] - out.shape[1]:] if self.gate else None, softcap=self.softcap or 0.0)
+                            gate=qkv[:, qkv.shape[1] - out.shape[1]:] if self.gate else None, softcap=self.softcap or 0.0,
+                            sinks=self.sinks)
+        if self.head_gate:
+            ops.head_gate(out, qkv[:, self.head_gate_col: self.head_gate_col + self.num_heads], self.num_heads, self.head_dim)
         if self.rotate_values:
             ops.turn_heads(out, ctx.positions, self.value_inv_freq, self.num_heads, self.head_dim, self.value_dim,
                            interleaved=getattr(self.position_encoding, "interleaved", False), sign=-1.0)

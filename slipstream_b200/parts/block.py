@@ -91,3 +91,36 @@ class BranchNormBlock(Block):
             else:
                 x = self.ffn_norm.add_branch(residual, out, want_out=hand_over)
         return residual, None, (x if hand_over else None)
+
+
+@BLOCKS.register("parallel_branches")
+class ParallelBlock(Block):
+    """``x + (mixer(norm(x)) + ffn(norm(x)))``: ONE norm whose output both branches read; their outputs are added to the
+    stream together.  ``feed_forward`` may be None.  ``norm`` is a `ConnectedNorm` (one stream: the plain residual
+    sum), whose kernel applies the block's pending pair of outputs where the next norm reads the stream."""
+
+    cuda_graph_safe = True
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norm: Norm) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norm = norm
+
+    def children(self) -> list[Part]:
+        return [p for p in (self.norm, self.mixer, self.feed_forward) if p is not None]
+
+    def forward(self, residual: torch.Tensor, pending, ctx, layer: LayerBinding):
+        residual, pending, _ = self.forward_chained(residual, pending, None, None, ctx, layer)
+        return residual, pending
+
+    def first_norm(self) -> Norm:
+        return self.norm
+
+    def forward_chained(self, residual: torch.Tensor, pending, normed, following: Norm | None, ctx, layer: LayerBinding):
+        if normed is not None:
+            x = normed if isinstance(normed, torch.Tensor) else normed.materialize()  # two branches read it
+        else:
+            x = self.norm.add_norm(residual, pending)
+        mixed = self.mixer.forward(x, ctx, layer)
+        fed = self.feed_forward.forward(x, ctx) if self.feed_forward is not None else None
+        return residual, self.norm.write_of(mixed, fed), None

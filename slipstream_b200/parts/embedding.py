@@ -100,9 +100,11 @@ class LMHead(Head):
     takes_pending_norm = True  # ``forward`` hands x to ``ops.linear`` as it is
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None,
-                 tensor: str | None = None, softcap: float | None = None) -> None:
-        """``softcap`` c: the logits leave as ``c * tanh(logits / c)``."""
+                 tensor: str | None = None, softcap: float | None = None, scale: float = 1.0) -> None:
+        """``scale``: the head's output is multiplied by it.  ``softcap`` c: the (scaled) logits leave as
+        ``c * tanh(logits / c)``."""
         self.softcap = float(softcap) if softcap else None
+        self.scale = float(scale)
         self.name = name
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
@@ -121,4 +123,6 @@ class LMHead(Head):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear(x, self.weight, None, out_dtype=torch.float32)
-        return ops.soft_cap(logits, self.softcap) if self.softcap else logits
+        if self.softcap or self.scale != 1.0:
+            return ops.soft_cap(logits, self.softcap, self.scale)
+        return logits

@@ -41,16 +41,17 @@ class LatentAttention(Mixer):
                  kv_rank: int, scale: float, position_encoding: PositionEncoding, norm_eps: float = 1e-6, *,
                  sinks: bool = True, gate: bool = True, has_kv: bool = True, page_size: int | None = None,
                  names: dict[str, str] | None = None) -> None:
-        """``position_encoding``: rotates the ``rot_dim`` part in half-split pairs (its table holds ``rot_dim / 2``
-        frequencies); a part without a table leaves it unrotated.  ``names``: the checkpoint's tensor names by role
+        """``position_encoding``: rotates the ``rot_dim`` part (its table holds ``rot_dim / 2`` frequencies; pairs of
+        halves, or of neighbours when the encoding says ``interleaved``); a part without a table leaves it unrotated.  ``names``: the checkpoint's tensor names by role
         (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, g, o)."""
         if min(heads, dim, value_dim, q_rank, kv_rank) < 1 or rot_dim < 0 or rot_dim % 2:
             raise ValueError("heads, dim, value_dim, q_rank and kv_rank must be >= 1, rot_dim even and >= 0")
         self.row = -(-(kv_rank + rot_dim) // 16) * 16  # elements of a cached row as the kernels see it
         if self.row > 256:
             raise ValueError("kv_rank + rot_dim must be at most 256")
-        if getattr(position_encoding, "interleaved", False):
-            raise ValueError("the rotated part is paired in halves")
+        # pairs of neighbours (2i, 2i + 1): the rows of the rotated part are reordered where the weights are bound, so that
+        # pair i sits at (i, i + rot_dim / 2); queries and keys are reordered alike, which leaves every score as it was
+        self.neighbour_pairs = bool(getattr(position_encoding, "interleaved", False))
         self.name, self.hidden_size = name, hidden_size
         self.heads, self.dim, self.rot_dim, self.value_dim = heads, dim, rot_dim, value_dim
         self.q_rank, self.kv_rank = q_rank, kv_rank
@@ -83,6 +84,16 @@ class LatentAttention(Mixer):
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         n, h = self.names, self.heads
+        if self.neighbour_pairs and self.rot_dim:
+            order = torch.cat([torch.arange(0, self.rot_dim, 2), torch.arange(1, self.rot_dim, 2)])
+            weights = dict(weights)
+            uq = weights[n["uq"]].reshape(h, self.dim + self.rot_dim, -1).clone()
+            uq[:, self.dim:] = uq[:, self.dim:][:, order.to(uq.device)]
+            weights[n["uq"]] = uq.reshape(h * (self.dim + self.rot_dim), -1)
+            if self.has_kv:
+                dkv = weights[n["dkv"]].clone()
+                dkv[self.kv_rank:] = dkv[self.kv_rank:][order.to(dkv.device)]
+                weights[n["dkv"]] = dkv
         # one product of the input: [query latent | key/value latent, shared key part | gates], padded to rows of
         # 16-byte multiples
         stacked = [weights[n["dq"]]] + ([weights[n["dkv"]]] if self.has_kv else []) + ([weights[n["g"]]] if self.gate else [])

@@ -105,8 +105,9 @@ class ActivatedFeedForward(FeedForward):
 
     ``activation`` "xielu": with two learned numbers p, q (the tensor ``act``, [2]),
     ``act(z) = softplus(p) z^2 + z / 2`` for z > 0 and ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` elsewhere; the two
-    coefficients are formed once where the weights are bound, in double precision.  ``names``: the checkpoint's tensor
-    names by role (up, down, act)."""
+    coefficients are formed once where the weights are bound, in double precision.  ``activation`` "relu2":
+    ``act(z) = relu(z)^2``, no tensor.  ``names``: the checkpoint's tensor names by
+    role (up, down, act)."""
 
     cuda_graph_safe = True
     takes_into = True
@@ -114,29 +115,35 @@ class ActivatedFeedForward(FeedForward):
 
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "xielu",
                  names: dict[str, str] | None = None) -> None:
-        if activation != "xielu":
-            raise ValueError(f"unknown activation {activation!r} (known: xielu)")
+        if activation not in ("xielu", "relu2"):
+            raise ValueError(f"unknown activation {activation!r} (known: xielu, relu2)")
         self.name, self.hidden_size, self.intermediate_size, self.activation = name, hidden_size, intermediate_size, activation
         self.names = {role: f"{name}.{role}" for role in ("up", "down", "act")}
         self.names.update(names or {})
 
     def weight_specs(self) -> list[WeightSpec]:
         n = self.names
-        return [WeightSpec(n["up"], (self.intermediate_size, self.hidden_size)),
-                WeightSpec(n["down"], (self.hidden_size, self.intermediate_size)),
-                WeightSpec(n["act"], (2,), kind="vector", init=("normal", 0.5))]
+        specs = [WeightSpec(n["up"], (self.intermediate_size, self.hidden_size)),
+                 WeightSpec(n["down"], (self.hidden_size, self.intermediate_size))]
+        if self.activation == "xielu":
+            specs.append(WeightSpec(n["act"], (2,), kind="vector", init=("normal", 0.5)))
+        return specs
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         self.up, self.down = weights[self.names["up"]], weights[self.names["down"]]
-        p, q = (float(v) for v in weights[self.names["act"]].to(torch.float64).cpu())
-        self.square_coeff, self.tail_coeff = _softplus(p), 0.5 + _softplus(q)
+        if self.activation == "xielu":
+            p, q = (float(v) for v in weights[self.names["act"]].to(torch.float64).cpu())
+            self.square_coeff, self.tail_coeff = _softplus(p), 0.5 + _softplus(q)
 
     def weight_bytes(self) -> int:
         return (self.up.numel() + self.down.numel()) * self.down.element_size()
 
     def forward(self, x: torch.Tensor, ctx, into: IntoNorm | None = None) -> torch.Tensor:
-        hidden = ops.xielu(ops.linear(x, self.up), self.square_coeff, self.tail_coeff)
+        if self.activation == "relu2":
+            hidden = ops.relu_square(ops.linear(x, self.up))
+        else:
+            hidden = ops.xielu(ops.linear(x, self.up), self.square_coeff, self.tail_coeff)
         if into is not None:
             return into.close(hidden, self.down, None)
         return ops.linear(hidden, self.down)

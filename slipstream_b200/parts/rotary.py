@@ -23,8 +23,9 @@ class RotaryEncoding(PositionEncoding):
     mscale = 1.0  # factor on every cosine and sine
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, interleaved: bool = False,
-                 exact_table: bool = False) -> None:
-        """``exact_table``: form the frequencies in double precision and round them once, instead of in float32.
+                 exact_table: bool = False, stretch: float = 1.0) -> None:
+        """``stretch``: every frequency is divided by it (positions stretched linearly; with ``exact_table``).
+        ``exact_table``: form the frequencies in double precision and round them once, instead of in float32.
         ``interleaved``: neighbouring elements (2i, 2i+1) form a pair instead of (i, i + rotary_dim/2).  The
         fused rotary kernels of the plain attention path take the half-split pairing only; an attention part
         asks ``plain`` before it uses them."""
@@ -33,6 +34,9 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         self.interleaved = bool(interleaved)
         self.exact_table = bool(exact_table)
+        self.stretch = float(stretch)
+        if not self.stretch > 0.0 or (self.stretch != 1.0 and not exact_table):
+            raise ValueError("stretch must be positive, and comes with exact_table")
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim must be even and in (0, {head_dim}], got {self.rotary_dim}")
         self.inv_freq: torch.Tensor | None = None
@@ -45,7 +49,7 @@ class RotaryEncoding(PositionEncoding):
     def inverse_frequencies(self) -> torch.Tensor:
         if self.exact_table:
             dims = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
-            return (self.theta ** (-dims / self.rotary_dim)).to(torch.float32)
+            return (self.theta ** (-dims / self.rotary_dim) / self.stretch).to(torch.float32)
         dims = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
         return 1.0 / (self.theta ** (dims / self.rotary_dim))
 

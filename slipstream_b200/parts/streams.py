@@ -30,11 +30,13 @@ from .base import BLOCKS, NORMS, Block, FeedForward, IntoNorm, LayerBinding, Mix
 
 @dataclass
 class StreamWrite:
-    """A branch output that has not been written into the streams yet, with its branch's write weights."""
+    """A branch output that has not been written into the streams yet, with its branch's write weights.  ``y2``: the
+    output of a second branch that read the same input; the two are added (in float32) where they are written."""
 
     y: torch.Tensor
     mix: torch.Tensor  # float32 [S, S], [from, to]
     out: torch.Tensor  # float32 [S]
+    y2: torch.Tensor | None = None
 
 
 @dataclass
@@ -102,9 +104,9 @@ class ConnectedNorm(Norm):
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def write_of(self, y: torch.Tensor) -> StreamWrite:
-        """``y`` as the output of the branch behind this norm."""
-        return StreamWrite(y, self.mix, self.w_out)
+    def write_of(self, y: torch.Tensor, y2: torch.Tensor | None = None) -> StreamWrite:
+        """``y`` (plus ``y2``, a second branch's) as the output of the branch behind this norm."""
+        return StreamWrite(y, self.mix, self.w_out, y2)
 
     def add_norm(self, residual: torch.Tensor, delta: "StreamWrite | None",
                  rows: torch.Tensor | None = None) -> torch.Tensor:
@@ -116,7 +118,7 @@ class ConnectedNorm(Norm):
         if delta is None:
             return ops.hc_norm(streams, None, None, None, self.w_in, self.weight, self.eps, self.runtime.dtype, rows=rows)
         return ops.hc_norm(streams, delta.y, delta.mix, delta.out, self.w_in, self.weight, self.eps, self.runtime.dtype,
-                           rows=rows)
+                           rows=rows, y2=delta.y2)
 
     def write_linear_then_norm(self, residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
                                bias: torch.Tensor | None, writer: "ConnectedNorm"):

@@ -74,7 +74,9 @@ def load_config(folder: str | Path) -> tuple[Architecture, ModelConfigBase]:
 def _register_builtin() -> None:
     from slipstream_b200.config.bezutar_config import BezutarConfig
     from slipstream_b200.config.fokedra_config import FokedraConfig
+    from slipstream_b200.config.lakadra_config import LakadraConfig
     from slipstream_b200.models.bezutar import build_bezutar
+    from slipstream_b200.models.lakadra import build_lakadra
     from slipstream_b200.models.fokedra import build_fokedra
     from slipstream_b200.config.sarudra_config import SarudraConfig
     from slipstream_b200.models.qwen2 import build_qwen2
@@ -84,6 +86,7 @@ def _register_builtin() -> None:
     register_architecture("Fokedra", FokedraConfig, build_fokedra)
     register_architecture("Sarudra", SarudraConfig, build_sarudra)
     register_architecture("Bezutar", BezutarConfig, build_bezutar)
+    register_architecture("Lakadra", LakadraConfig, build_lakadra)
 
 
 _register_builtin()
