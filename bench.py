@@ -23,6 +23,10 @@ one, grouped norms on the branches' outputs).
 state, latent attention over one cached row per token with sinks, a convolution over every mixer's input, an embedding
 summed from three tables, hyper-connected streams, a feed-forward without a gate branch).
 
+``--compare lakadra`` does the same for the Lakadra decoder (linear attention with a decay per head, latent attention,
+windowed attention with a unit sink beside a gated linear recurrence, un-gated routed experts with groups, pass-through
+experts and a gated shared expert, one norm for both branches of a layer).
+
 ``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
 headline): ``--only decode --batch 1 --prompt-len 32000 --context-len 32768`` is a decode step behind a long
 context, ``--only prefill --chunk 512 --prefix 8192 --context-len 32768`` a prompt portion behind cached tokens.
@@ -442,7 +446,8 @@ def measure_model(config: dict, args, pk: dict, rng) -> dict:
     for block in runner.model.blocks:
         ffn = getattr(block, "feed_forward", None)
         if hasattr(ffn, "experts"):
-            per_expert = (ffn.gate_up[0].numel() + ffn.down[0].numel()) * ffn.down.element_size()
+            first = ffn.gate_up if getattr(ffn, "gated", True) else ffn.up
+            per_expert = (first[0].numel() + ffn.down[0].numel()) * ffn.down.element_size()
             nbytes += (min(ffn.experts, batch * ffn.top) - ffn.top) * per_expert
     for entry, state in zip(runner.model.order, runner.store.state):
         nbytes += 2 * batch * sum(t[0].numel() * t.element_size() for t in state.values())
@@ -1058,6 +1063,231 @@ def run_compare_bezutar(args) -> int:
     return 0
 
 
+def lakadra_config(z: dict, window: int) -> dict:
+    """config.json of a Lakadra decoder at the layer sizes ``z``: a decayed linear-attention layer, a latent-attention
+    layer, a pair of windowed attention and gated linear recurrence, and a latent-attention layer that reads the rows of
+    the other, in turn.  Linear attention has the attention's heads and head size; latent attention caches 96 + 32
+    elements a token; the recurrence has the model's width in blocks of 256.  Every feed-forward is routed: two of eight
+    un-gated experts (and two pass-through experts) in five groups of which three are kept, beside a shared expert,
+    sized so that a token's feed-forward does the work of the dense gated one."""
+    rot = dict(base=1000000.0, dims=32)
+    ff_e, ff_s = z["ff"] * 3 // 8 // 64 * 64, z["ff"] * 3 // 4 // 64 * 64
+    mlp = dict(kind="moe", expert=dict(ff=ff_e), shared=dict(ff=ff_s),
+               router=dict(experts=8, identity=2, top=2, groups=dict(count=5, keep=3)))
+    layers = []
+    for i in range(z["layers"]):
+        if i % 4 == 0:
+            kind = "lightning"
+            mixer = dict(heads=z["heads"], dim=z["dim"], vdim=z["dim"], decay=[1.0 - 2.0 ** -(2 + 6 * h / z["heads"]) for h in range(z["heads"])])
+        elif i % 4 == 2:
+            kind = "parallel"
+            mixer = dict(left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+                                   mask=dict(size=window), rot=dict(base=1000000.0, dims=z["dim"] // 2, scaling=dict(factor=8.0))),
+                         right=dict(width=z["width"], blocks=z["width"] // 256 if z["width"] % 256 == 0 else z["width"] // 128, conv=4),
+                         left_scale=1.2, right_scale=0.9)
+        else:
+            kind = "latent_attention"
+            mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=32, vdim=z["dim"], q_rank=max(z["width"] // 4, 256) // 64 * 64,
+                         kv_rank=96, scale=(z["dim"] + 32) ** -0.5, rot=rot)
+            if i % 4 == 3:
+                mixer["kv_from"] = i - 2
+        layers.append(dict(type=kind, mixer=mixer, mlp=mlp))
+    return dict(architecture="Lakadra", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), logit_scale=2.0,
+                logit_softcap=30.0, layers=layers, max_position_embeddings=8192)
+
+
+def run_compare_lakadra(args) -> int:
+    """The Lakadra decoder beside the Qwen2.5 decoder at equal layer sizes (whole steps), then every kernel the design
+    adds, alone at the 7B layer sizes, beside its nearest relative among the kernels of the other decoders."""
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import ops
+
+    pk, pk_kind = peaks()
+    rng = np.random.default_rng(0)
+    dev = torch.device("cuda:0")
+    batch, ctx_tokens, T = args.batch, args.prompt_len, args.chunk
+    result: dict = {"compare": "lakadra", "peaks": pk_kind, "batch": batch, "context": ctx_tokens, "prefill_tokens": T,
+                    "window": args.window, "sizes": {}}
+    for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
+        qwen, _ = compare_configs(COMPARE_SIZES[name], 8192, 1, False)
+        result["sizes"][name] = {}
+        for which, config in (("qwen2", qwen), ("lakadra", lakadra_config(COMPARE_SIZES[name], args.window))):
+            if which == "qwen2" and args.skip_qwen2:
+                continue
+            print(f"[bench] {name} {which} ...", file=sys.stderr, flush=True)
+            result["sizes"][name][which] = measure_model(config, args, pk, rng)
+            print(f"[bench] {name} {which}: {result['sizes'][name][which]}", file=sys.stderr, flush=True)
+    if args.no_kernels:
+        print(json.dumps(result))
+        return 0
+
+    print("[bench] single kernels ...", file=sys.stderr, flush=True)
+    z = COMPARE_SIZES["7b"]
+    h, n_q, d, inter = z["width"], z["heads"], z["dim"], z["ff"]
+    cfg = lakadra_config(z, args.window)
+    ff_e, ff_s = cfg["layers"][0]["mlp"]["expert"]["ff"], cfg["layers"][0]["mlp"]["shared"]["ff"]
+    blocks = cfg["layers"][2]["mixer"]["right"]["blocks"]
+    bs = h // blocks
+    gen = torch.Generator(device=dev).manual_seed(1)
+    COPIES = 6  # operands of each timed launch rotate through this many copies
+
+    def rand(*shape, dtype=torch.bfloat16, std=0.5):
+        return (torch.randn(*shape, generator=gen, device=dev) * std).to(dtype)
+
+    def sweep(run, copies=COPIES) -> float:
+        for i in range(copies):
+            run(i)
+        times = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(copies):
+                run(i)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / copies)
+        return sorted(times)[2]
+
+    kernels: dict = {}
+
+    def hbm(name: str, us: float, nbytes: float, **more) -> None:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        kernels[name] = {"us": round(us, 2), "gbs": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 3), **more}
+
+    def tensor(name: str, us: float, flops: float) -> None:
+        tf = flops / (us * 1e-6) / 1e12
+        kernels[name] = {"us": round(us, 2), "tflops": round(tf, 1), "bf16_frac": round(tf / pk["bf16_tflops"], 3)}
+
+    def step(q_lens, seq_lens):
+        starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+        as_dev = lambda v: torch.tensor(np.asarray(v), dtype=torch.int32, device=dev)  # noqa: E731
+        positions = np.concatenate([np.arange(s - n, s) for n, s in zip(q_lens, seq_lens)])
+        return types.SimpleNamespace(q_start=as_dev(starts), seq_lens=as_dev(seq_lens), state_slots=as_dev(np.arange(len(q_lens))),
+                                     positions=as_dev(positions), num_requests=len(q_lens),
+                                     is_decode_only=all(n == 1 for n in q_lens))
+
+    one = torch.ones(1, device=dev)
+    for tokens, tag, ctx in ((T, "prefill", step([T], [T])), (batch, "decode", step([1] * batch, [ctx_tokens] * batch))):
+        R = ctx.num_requests
+        # the norm in front of a layer, which adds the two outputs of the layer before; beside the add + norm of one
+        streams = [rand(tokens, 1, h, dtype=torch.float32) for _ in range(COPIES)]
+        ys, y2s = [rand(tokens, h) for _ in range(COPIES)], [rand(tokens, h) for _ in range(COPIES)]
+        w_norm = rand(h, dtype=torch.float32)
+        us = sweep(lambda i: ops.add_rmsnorm(streams[i][:, 0], ys[i], w_norm, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_add_rmsnorm (qwen2)", us, tokens * h * (4 + 4 + 2 + 2))
+        us = sweep(lambda i: ops.hc_norm(streams[i], ys[i], one.view(1, 1), one, None, w_norm, 1e-6, torch.bfloat16, y2=y2s[i]))
+        hbm(f"{tag}_norm that adds two outputs", us, tokens * h * (4 + 4 + 2 + 2 + 2))
+        del streams, y2s
+        # linear attention with a decay per head and its gated norm, beside the matrix memory of equal state
+        qkvg = [rand(tokens, n_q * 4 * d) for _ in range(COPIES)]
+        decay = torch.full((n_q,), 0.99, device=dev)
+        memory = [torch.zeros(R, n_q, d, d, device=dev) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.decay_attention(qkvg[i], decay, memory[i], ctx, n_q, d, d))
+        hbm(f"{tag}_decay_attention", us, R * n_q * d * d * 8.0 + tokens * n_q * d * (3 * 2.0 + 4.0),
+            fp32_tflops=round(4.0 * tokens * n_q * d * d / us / 1e6, 2))
+        gates = [rand(tokens, 2 * n_q, dtype=torch.float32, std=3.0) for _ in range(COPIES)]
+        bias = rand(n_q, dtype=torch.float32)
+        memory1 = [torch.zeros(R, n_q, d + 1, d, device=dev) for _ in range(COPIES)]
+        peak = torch.zeros(R, n_q, device=dev)
+        us = sweep(lambda i: ops.matrix_cell(qkvg[i], gates[i], bias, bias, 15.0, d ** -0.5, memory1[i], peak, ctx, n_q, d, d))
+        hbm(f"{tag}_matrix_cell of equal state (bezutar)", us, R * n_q * (d + 1) * d * 8.0 + tokens * n_q * d * (3 * 2.0 + 4.0),
+            fp32_tflops=round(6.0 * tokens * n_q * (d + 1) * d / us / 1e6, 2))
+        num, nq, peaks_t = ops.matrix_cell(qkvg[0], gates[0], bias, bias, 15.0, d ** -0.5, memory1[0], peak, ctx, n_q, d, d)
+        w_cell = rand(n_q * d, dtype=torch.float32)
+        us = sweep(lambda i: ops.cell_output(num, nq, peaks_t, w_cell, qkvg[i][:, 3 * n_q * d:], n_q, d, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_cell_output (bezutar: head norm, gate)", us, tokens * n_q * d * (4.0 + 2.0 + 2.0))
+        mixed = ops.decay_attention(qkvg[0], decay, memory[0], ctx, n_q, d, d)
+        us = sweep(lambda i: ops.gated_rmsnorm(mixed, qkvg[i][:, 3 * n_q * d:], w_cell, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_gated_rmsnorm (norm over all heads, gate)", us, tokens * n_q * d * (4.0 + 2.0 + 2.0))
+        del qkvg, gates, memory, memory1, num, mixed
+        # the gated linear recurrence: convolution, gates from square blocks, the recurrence; beside the gated recurrence
+        # per channel of the Bezutar decoder
+        projs = [rand(tokens, 2 * h) for _ in range(COPIES)]
+        w_taps, b_taps = rand(h, 4, dtype=torch.float32), rand(h, dtype=torch.float32)
+        conv_state = torch.zeros(R, 3, h, device=dev)
+        us = sweep(lambda i: ops.conv_silu(projs[i], h, h, w_taps, b_taps, conv_state, ctx, activation=False))
+        hbm(f"{tag}_convolution (no activation)", us, tokens * h * 4.0 + R * 3 * h * 8.0)
+        us = sweep(lambda i: ops.conv_silu(projs[i], h, h, w_taps, b_taps, conv_state, ctx))
+        hbm(f"{tag}_conv_silu (sarudra)", us, tokens * h * 4.0 + R * 3 * h * 8.0)
+        us_ = [rand(tokens, h) for _ in range(COPIES)]
+        gate_w = rand(blocks, 2 * bs, bs, std=0.05)
+        us = sweep(lambda i: ops.block_gates(us_[i], gate_w))
+        flops = 4.0 * tokens * h * bs
+        moved = tokens * h * (2.0 + 8.0) + gate_w.numel() * 2.0
+        kernels[f"{tag}_block_gates ({blocks} blocks of {bs})"] = {
+            "us": round(us, 2), "tflops": round(flops / us / 1e6, 2), "bf16_frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3),
+            "gbs": round(moved / us / 1e3, 1), "hbm_frac": round(moved / us / 1e3 / pk["hbm_gbs"], 3)}
+        pre = ops.block_gates(us_[0], gate_w)
+        gate_b, lam = rand(blocks, 2 * bs, dtype=torch.float32), rand(h, dtype=torch.float32)
+        cell = torch.zeros(R, h, device=dev)
+        us = sweep(lambda i: ops.gated_linear_recurrence(pre, gate_b, us_[i], projs[i][:, :h], lam, 8.0, cell, ctx))
+        hbm(f"{tag}_gated_linear_recurrence", us, tokens * h * (8.0 + 3 * 2.0) + R * h * 8.0)
+        projs3 = [rand(tokens, 3 * h) for _ in range(COPIES)]
+        bias2 = rand(2 * h, dtype=torch.float32)
+        us = sweep(lambda i: ops.gated_recurrence(projs3[i], h, cell, ctx, bias=bias2))
+        hbm(f"{tag}_gated_recurrence (bezutar)", us, tokens * h * (3 * 2.0 + 2.0) + R * h * 8.0)
+        del projs, projs3, us_, pre
+        # small kernels around the attention of a pair of mixers
+        outs = [rand(tokens, n_q * d) for _ in range(COPIES)]
+        hg = rand(tokens, 32)
+        us = sweep(lambda i: ops.head_gate(outs[i], hg[:, :n_q], n_q, d))
+        hbm(f"{tag}_head_gate (in place)", us, tokens * n_q * d * 4.0)
+        us = sweep(lambda i: ops.sigmoid_gate(outs[i], outs[(i + 1) % COPIES]))
+        hbm(f"{tag}_sigmoid_gate (fokedra, in place)", us, tokens * n_q * d * 6.0)
+        us = sweep(lambda i: ops.scaled_sum(ys[i], 1.2, ys[(i + 1) % COPIES], 0.9))
+        hbm(f"{tag}_scaled_sum of two mixers", us, tokens * h * 6.0)
+        del outs
+        # the routed feed-forward: router, experts, weighted sum; beside the gated experts of the Sarudra decoder of
+        # equal work (two of eight, expert size a quarter of the dense one)
+        xs = [rand(tokens, h) for _ in range(COPIES)]
+        w_router = rand(11, h, std=0.05)
+        corr = rand(10, dtype=torch.float32, std=0.05)
+        us = sweep(lambda i: ops.router(xs[i], w_router, 2, softmax=True, correction=corr, groups=5, keep=3, extra=1))
+        kernels[f"{tag}_router (softmax, correction, groups, a gate's row)"] = {"us": round(us, 2)}
+        w8 = w_router[:8].contiguous()
+        us = sweep(lambda i: ops.router(xs[i], w8, 2))
+        kernels[f"{tag}_router (sarudra: sigmoid)"] = {"us": round(us, 2)}
+        ids, scores, sg = ops.router(xs[0], w_router, 2, softmax=True, correction=corr, groups=5, keep=3, extra=1)
+        up, down = rand(8, ff_e, h, std=0.02), rand(8, h, ff_e, std=0.02)
+        us = sweep(lambda i: ops.moe_experts_single(xs[i], ids, up, down, 10))
+        touched = int(torch.unique(ids[ids < 8]).numel())
+        flops = 4.0 * int((ids < 8).sum()) * h * ff_e
+        moved = touched * 2 * ff_e * h * 2.0
+        kernels[f"{tag}_un-gated experts (plan, gather, up, down)"] = {
+            "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "bf16_frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3),
+            "gbs": round(moved / us / 1e3, 1), "hbm_frac": round(moved / us / 1e3 / pk["hbm_gbs"], 3), "experts_touched": touched}
+        ff_g = inter // 4 // 64 * 64
+        gate_up, down_g = rand(8, 2 * ff_g, h, std=0.02), rand(8, h, ff_g, std=0.02)
+        ids8, scores8 = ops.router(xs[0], w8, 2)
+        us = sweep(lambda i: ops.moe_experts(xs[i], ids8, scores8, gate_up, down_g, 64))
+        touched8 = int(torch.unique(ids8).numel())
+        flops = 6.0 * tokens * 2 * h * ff_g
+        moved = touched8 * 3 * ff_g * h * 2.0
+        kernels[f"{tag}_gated experts of equal work (sarudra)"] = {
+            "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "bf16_frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3),
+            "gbs": round(moved / us / 1e3, 1), "hbm_frac": round(moved / us / 1e3 / pk["hbm_gbs"], 3), "experts_touched": touched8}
+        y, term_rows = ops.moe_experts_single(xs[0], ids, up, down, 10)
+        shared = rand(tokens, h)
+        us = sweep(lambda i: ops.moe_mix(y, term_rows, ids, scores, 8, xs[i], shared, sg))
+        hbm(f"{tag}_moe_mix (weights, pass-through, gated shared expert)", us, tokens * h * (2 * (2.0 if term_rows is not None else 4.0) + 6.0))
+        y8, rows8 = ops.moe_experts(xs[0], ids8, scores8, gate_up, down_g, 64)
+        us = sweep(lambda i: ops.moe_combine(y8, shared, torch.bfloat16, rows8, 2))
+        hbm(f"{tag}_moe_combine (sarudra)", us, tokens * h * (2 * (2.0 if rows8 is not None else 4.0) + 4.0))
+        ups = [rand(tokens, ff_s) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.relu_square(ups[i]))
+        hbm(f"{tag}_relu_square", us, tokens * ff_s * 4.0)
+        us = sweep(lambda i: ops.xielu(ups[i], 0.7, 1.2))
+        hbm(f"{tag}_xielu (bezutar)", us, tokens * ff_s * 4.0)
+        del xs, ups, y, y8, up, down, gate_up, down_g, ys
+    ops.check_errors(dev)
+    result["kernels_7b"] = kernels
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1077,7 +1307,7 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
     ap.add_argument("--window", type=int, default=4096, help="--compare sarudra: positions of the sliding window")
-    ap.add_argument("--compare", choices=["fokedra", "sarudra", "bezutar"], default=None,
+    ap.add_argument("--compare", choices=["fokedra", "sarudra", "bezutar", "lakadra"], default=None,
                     help="time another decoder design beside the Qwen2.5 decoder at equal layer sizes instead")
     ap.add_argument("--sizes", default="", help="--compare: which of 0.5b,7b,14b (default: all)")
     ap.add_argument("--mask-chunk", type=int, default=8192, help="--compare: positions per attention chunk")
@@ -1099,6 +1329,8 @@ def main() -> int:
         args.warmup = max(args.warmup, 3)
         if args.compare == "bezutar":
             return run_compare_bezutar(args)
+        if args.compare == "lakadra":
+            return run_compare_lakadra(args)
         return run_compare_sarudra(args) if args.compare == "sarudra" else run_compare(args)
     if args.workload:
         return run_workload(args.workload, args)

@@ -16,7 +16,6 @@
 namespace {
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -29,17 +28,27 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // proj row: [q: heads * dim | k: heads * dim | v: heads * vdim | ...] (pre-activations).  Per request and head, token
 // by token:  S <- decay S + silu(k) silu(v)^T,  o = S^T silu(q).  state: float32 [slots][heads][vdim][dim];
 // out: float32 [rows][heads * vdim].  A block takes one head of one request and DA_COLS value columns; a column is
-// held by DA_LANES lanes, each with every DA_LANES-th row of it in registers; tokens are staged DA_BATCH at a time.
+// held by DA_LANES lanes, each with groups of four neighbouring rows of it in registers (lane s has the groups s,
+// s + DA_LANES, ...), so that q and k come from shared memory sixteen bytes a load; tokens are staged DA_BATCH at a
+// time with their activation applied, and the dot products of four tokens are reduced over the lanes together.
+// FAST (the bfloat16 rows): the activation with the approximate exponential and division, whose error is far below
+// the rounding of the projected values.
 #define DA_LANES 8
 #define DA_COLS 32
 #define DA_BATCH 16
 #define DA_MAX_DIM 256
 
-template <typename T, int RMAX>
+template <bool FAST>
+__device__ __forceinline__ float silu_act(float z) {
+    return FAST ? __fdividef(z, 1.0f + __expf(-z)) : z / (1.0f + expf(-z));
+}
+
+template <typename T, int RMAX, bool FAST>
 __global__ void __launch_bounds__(DA_LANES * DA_COLS)
 decay_attention_kernel(const T* __restrict__ proj, int64_t stride, const float* __restrict__ decay, float* __restrict__ state,
                        float* __restrict__ out, const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                        const int32_t* __restrict__ slots, int heads, int dim, int vdim, int n_slots, int* err) {
+    constexpr int GROUPS = RMAX / 4;
     const int col_blocks = (vdim + DA_COLS - 1) / DA_COLS;
     const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks, r = blockIdx.y;
     const float d = decay[h];
@@ -51,53 +60,77 @@ decay_attention_kernel(const T* __restrict__ proj, int64_t stride, const float* 
         if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         return;
     }
-    __shared__ float qs[DA_BATCH][DA_MAX_DIM], ks[DA_BATCH][DA_MAX_DIM], vs[DA_BATCH][DA_COLS];
+    __shared__ __align__(16) float qs[DA_BATCH][DA_MAX_DIM], ks[DA_BATCH][DA_MAX_DIM];
+    __shared__ float vs[DA_BATCH][DA_COLS];
     const int tid = threadIdx.x, sub = tid % DA_LANES, col = tid / DA_LANES, j = cb * DA_COLS + col;
     const bool live = j < vdim;
+    const int dim4 = (dim + 3) & ~3;  // rows behind the head's last one are zeros in shared memory
     float* sp = state + (((int64_t)slot * heads + h) * vdim + (live ? j : 0)) * dim;
     float S[RMAX];
 #pragma unroll
-    for (int i = 0; i < RMAX; ++i) {
-        const int row = sub + i * DA_LANES;
-        S[i] = (live && row < dim) ? sp[row] : 0.f;
-    }
+    for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int row = 4 * (sub + g * DA_LANES) + e;
+            S[4 * g + e] = (live && row < dim) ? sp[row] : 0.f;
+        }
     const int64_t k_off = (int64_t)heads * dim + (int64_t)h * dim, v_off = 2 * (int64_t)heads * dim + (int64_t)h * vdim;
     for (int t0 = 0; t0 < q_len; t0 += DA_BATCH) {
         const int nb = min(DA_BATCH, q_len - t0);
         __syncthreads();
-        for (int i = tid; i < nb * dim; i += blockDim.x) {
-            const int t = i / dim, e = i - t * dim;
+        for (int i = tid; i < nb * dim4; i += blockDim.x) {
+            const int t = i / dim4, e = i - t * dim4;
             const T* row = proj + (int64_t)(q0 + t0 + t) * stride;
-            qs[t][e] = silu_f(to_float(row[(int64_t)h * dim + e]));
-            ks[t][e] = silu_f(to_float(row[k_off + e]));
+            qs[t][e] = e < dim ? silu_act<FAST>(to_float(row[(int64_t)h * dim + e])) : 0.f;
+            ks[t][e] = e < dim ? silu_act<FAST>(to_float(row[k_off + e])) : 0.f;
         }
         for (int i = tid; i < nb * DA_COLS; i += blockDim.x) {
             const int t = i / DA_COLS, e = i - t * DA_COLS;
-            vs[t][e] = cb * DA_COLS + e < vdim ? silu_f(to_float(proj[(int64_t)(q0 + t0 + t) * stride + v_off + cb * DA_COLS + e])) : 0.f;
+            vs[t][e] = cb * DA_COLS + e < vdim ? silu_act<FAST>(to_float(proj[(int64_t)(q0 + t0 + t) * stride + v_off + cb * DA_COLS + e])) : 0.f;
         }
         __syncthreads();
-        for (int t = 0; t < nb; ++t) {
-            const float v = vs[t][col];
-            float acc = 0.f;
+        for (int t = 0; t < nb; t += 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < RMAX; ++i) {
-                const int row = sub + i * DA_LANES;
-                if (row < dim) {
-                    S[i] = fmaf(ks[t][row], v, d * S[i]);
-                    acc = fmaf(S[i], qs[t][row], acc);
+            for (int w = 0; w < 4; ++w) {
+                if (t + w >= nb) break;
+                const float v = vs[t + w][col];
+#pragma unroll
+                for (int g = 0; g < GROUPS; ++g) {
+                    const int at = 4 * (sub + g * DA_LANES);
+                    if (at < dim4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(&ks[t + w][at]);
+                        const float4 q4 = *reinterpret_cast<const float4*>(&qs[t + w][at]);
+                        S[4 * g + 0] = fmaf(k4.x, v, d * S[4 * g + 0]);
+                        S[4 * g + 1] = fmaf(k4.y, v, d * S[4 * g + 1]);
+                        S[4 * g + 2] = fmaf(k4.z, v, d * S[4 * g + 2]);
+                        S[4 * g + 3] = fmaf(k4.w, v, d * S[4 * g + 3]);
+                        acc[w] = fmaf(S[4 * g + 0], q4.x, acc[w]);
+                        acc[w] = fmaf(S[4 * g + 1], q4.y, acc[w]);
+                        acc[w] = fmaf(S[4 * g + 2], q4.z, acc[w]);
+                        acc[w] = fmaf(S[4 * g + 3], q4.w, acc[w]);
+                    }
                 }
             }
 #pragma unroll
-            for (int o = DA_LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (sub == 0 && live) out[(int64_t)(q0 + t0 + t) * heads * vdim + (int64_t)h * vdim + j] = acc;
+            for (int o = DA_LANES / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc[w] += __shfl_xor_sync(0xffffffffu, acc[w], o);
+            if (sub == 0 && live) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                    if (t + w < nb) out[(int64_t)(q0 + t0 + t + w) * heads * vdim + (int64_t)h * vdim + j] = acc[w];
+            }
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < RMAX; ++i) {
-            const int row = sub + i * DA_LANES;
-            if (row < dim) sp[row] = S[i];
-        }
+        for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = 4 * (sub + g * DA_LANES) + e;
+                if (row < dim) sp[row] = S[4 * g + e];
+            }
     }
 }
 
@@ -107,16 +140,16 @@ extern "C" int ss_decay_attention(const void* proj, int64_t stride, const float*
     if (R <= 0) return 0;
     if (heads < 1 || dim < 1 || dim > DA_MAX_DIM || vdim < 1) return (int)cudaErrorInvalidValue;
     const dim3 grid(heads * ((vdim + DA_COLS - 1) / DA_COLS), R), block(DA_LANES * DA_COLS);
-#define DA_GO(T, RMAX)                                                                                                  \
-    ss_launch(decay_attention_kernel<T, RMAX>, grid, block, 0, stream, (const T*)proj, stride, decay, state, out, q_start, \
-              seq_lens, slots, heads, dim, vdim, n_slots, err)
-#define DA_PICK(T)                                                                                                      \
+#define DA_GO(T, RMAX, FAST)                                                                                              \
+    ss_launch(decay_attention_kernel<T, RMAX, FAST>, grid, block, 0, stream, (const T*)proj, stride, decay, state, out,    \
+              q_start, seq_lens, slots, heads, dim, vdim, n_slots, err)
+#define DA_PICK(T, FAST)                                                                                                \
     do {                                                                                                                \
-        if (dim <= 8 * DA_LANES) DA_GO(T, 8);                                                                           \
-        else if (dim <= 16 * DA_LANES) DA_GO(T, 16);                                                                    \
-        else DA_GO(T, 32);                                                                                              \
+        if (dim <= 8 * DA_LANES) DA_GO(T, 8, FAST);                                                                     \
+        else if (dim <= 16 * DA_LANES) DA_GO(T, 16, FAST);                                                              \
+        else DA_GO(T, 32, FAST);                                                                                        \
     } while (0)
-    if (dtype == SS_BF16) DA_PICK(bf16); else DA_PICK(float);
+    if (dtype == SS_BF16) DA_PICK(bf16, true); else DA_PICK(float, false);
 #undef DA_PICK
 #undef DA_GO
     return SS_LAUNCH_CHECK();
@@ -217,57 +250,117 @@ extern "C" int ss_block_gates(const void* u, int64_t u_stride, const void* W, co
 
 // ---------------------------------------------------------------- the real-gated linear recurrence
 //
-// Per request and channel c = b bs + o, token by token, with pre[b][row] = [first gate: bs | second gate: bs] (float32,
-// their biases added where `bias` is given):
+// Per request and channel c = b bs + o, token by token, with pre[b][row] = [first gate: bs | second gate: bs] (float32;
+// their biases are added here where `bias` is given):
 //   r = sigmoid(pre1),  i = sigmoid(pre2),  a = exp(-rate r softplus(lam[c])),  S <- a S + sqrt(1 - a^2) i u,
 //   out = S * gelu_tanh(y)            (y: a view of the projection, rows y_stride apart; u [rows][C])
-// state float32 [slots][C].  A thread per request and channel.
+// state float32 [slots][C].
+//
+// A block takes one request and 32 neighbouring channels (a lane each, so that a warp reads whole lines) and cuts the
+// request's rows of this step into one segment per warp.  The recurrence is linear in S: a warp first walks its segment
+// from S = 0, which gives the segment's map S -> A S + B (and leaves every token's a and b in place of its two gate
+// values); the maps of the segments in front, applied in order to the request's state, give the warp its start; the
+// second walk is the recurrence as written and writes the outputs.  With one warp (a decode step) the first walk
+// starts from the state itself.  The same algebra however a request is cut; the roundings differ with the segments.
+#define GL_MAX_SEGS 16
 template <typename T>
-__global__ void __launch_bounds__(128)
-gated_linear_recurrence_kernel(const float* __restrict__ pre, const float* __restrict__ bias, const T* __restrict__ u,
+__global__ void __launch_bounds__(32 * GL_MAX_SEGS)
+gated_linear_recurrence_kernel(float* __restrict__ pre, const float* __restrict__ bias, const T* __restrict__ u,
                                const T* __restrict__ y, int64_t y_stride, const float* __restrict__ lam, float rate,
                                float* __restrict__ state, T* __restrict__ out, const int32_t* __restrict__ q_start,
                                const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ slots, int n_rows, int C,
                                int bs, int n_slots, int* err) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
-    const int b = c < C ? c / bs : 0, o = c < C ? c - b * bs : 0;
-    const float neg = c < C ? -rate * softplus_f(lam[c]) : 0.f;
-    const float b1 = (bias && c < C) ? bias[(int64_t)b * 2 * bs + o] : 0.f, b2 = (bias && c < C) ? bias[(int64_t)b * 2 * bs + bs + o] : 0.f;
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5, n_segs = blockDim.x >> 5;
+    const int c = blockIdx.x * 32 + lane, r = blockIdx.y;
+    const bool live = c < C;
+    const int b = live ? c / bs : 0, o = live ? c - b * bs : 0;
+    const float neg = live ? -rate * softplus_f(lam[c]) : 0.f;
+    const float b1 = (bias && live) ? bias[(int64_t)b * 2 * bs + o] : 0.f, b2 = (bias && live) ? bias[(int64_t)b * 2 * bs + bs + o] : 0.f;
     pdl_wait();
+    __shared__ float seg_a[GL_MAX_SEGS][32], seg_b[GL_MAX_SEGS][32];
     const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
-    if (c >= C || q_len <= 0 || seq_lens[r] <= 0) return;
+    if (q_len <= 0 || seq_lens[r] <= 0) return;
     const int slot = slots[r];
     if (slot < 0 || slot >= n_slots) {
         if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         return;
     }
-    float S = state[(int64_t)slot * C + c];
-    const float* p = pre + ((int64_t)b * n_rows + q0) * 2 * bs + o;
-    for (int t = 0; t < q_len; ++t) {
-        const float g1 = sigmoid_f(p[(int64_t)t * 2 * bs] + b1), g2 = sigmoid_f(p[(int64_t)t * 2 * bs + bs] + b2);
-        const float uv = to_float(u[(int64_t)(q0 + t) * C + c]);
-        const float la = neg * g1;
-        const float a = expf(la);
-        // 1 - a^2 without cancellation where a is close to one
-        const float keep = sqrtf(-expm1f(2.0f * la));
-        S = fmaf(a, S, keep * (g2 * uv));
-        out[(int64_t)(q0 + t) * C + c] = from_float<T>(S * gelu_tanh_f(to_float(y[(int64_t)(q0 + t) * y_stride + c])));
+    const int per = (q_len + n_segs - 1) / n_segs;
+    const int t0 = min(q_len, seg * per), t1 = min(q_len, t0 + per);
+    float* p = pre + ((int64_t)b * n_rows + q0) * 2 * bs + o;
+    const float s_init = live ? state[(int64_t)slot * C + c] : 0.f;
+    float A = 1.f, S = n_segs == 1 ? s_init : 0.f;
+    if (live) {
+        for (int t = t0; t < t1; t += 4) {  // the loads of four tokens are in flight together
+            float z1[4], z2[4], uv[4], yv[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int tt = min(t + w, t1 - 1);
+                z1[w] = p[(int64_t)tt * 2 * bs];
+                z2[w] = p[(int64_t)tt * 2 * bs + bs];
+                uv[w] = to_float(u[(int64_t)(q0 + tt) * C + c]);
+                yv[w] = n_segs == 1 ? to_float(y[(int64_t)(q0 + tt) * y_stride + c]) : 0.f;
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                if (t + w >= t1) break;
+                const float g1 = sigmoid_f(z1[w] + b1), g2 = sigmoid_f(z2[w] + b2);
+                const float la = neg * g1;
+                const float a = expf(la);
+                const float add = sqrtf(-expm1f(2.0f * la)) * (g2 * uv[w]);  // 1 - a^2 without cancellation where a is close to one
+                S = fmaf(a, S, add);
+                if (n_segs == 1) {
+                    out[(int64_t)(q0 + t + w) * C + c] = from_float<T>(S * gelu_tanh_f(yv[w]));
+                } else {
+                    p[(int64_t)(t + w) * 2 * bs] = a;
+                    p[(int64_t)(t + w) * 2 * bs + bs] = add;
+                    A *= a;
+                }
+            }
+        }
     }
-    state[(int64_t)slot * C + c] = S;
+    if (n_segs == 1) {
+        if (live) state[(int64_t)slot * C + c] = S;
+        return;
+    }
+    seg_a[seg][lane] = A;
+    seg_b[seg][lane] = S;
+    __syncthreads();
+    S = s_init;
+    for (int v = 0; v < seg; ++v) S = fmaf(seg_a[v][lane], S, seg_b[v][lane]);
+    if (!live) return;
+    for (int t = t0; t < t1; t += 4) {
+        float av[4], bv[4], yv[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int tt = min(t + w, t1 - 1);
+            av[w] = p[(int64_t)tt * 2 * bs];
+            bv[w] = p[(int64_t)tt * 2 * bs + bs];
+            yv[w] = to_float(y[(int64_t)(q0 + tt) * y_stride + c]);
+        }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            if (t + w >= t1) break;
+            S = fmaf(av[w], S, bv[w]);
+            out[(int64_t)(q0 + t + w) * C + c] = from_float<T>(S * gelu_tanh_f(yv[w]));
+        }
+    }
+    // the warp with the request's last token leaves the state
+    if (t1 == q_len && t0 < t1) state[(int64_t)slot * C + c] = S;
 }
 
-extern "C" int ss_gated_linear_recurrence(const float* pre, const float* bias, const void* u, const void* y, int64_t y_stride,
+extern "C" int ss_gated_linear_recurrence(float* pre, const float* bias, const void* u, const void* y, int64_t y_stride,
                                           const float* lam, float rate, float* state, void* out, const int32_t* q_start,
                                           const int32_t* seq_lens, const int32_t* slots, int R, int n_rows, int C, int bs,
-                                          int n_slots, int dtype, int* err, cudaStream_t stream) {
+                                          int n_slots, int dtype, int* err, cudaStream_t stream, int segments) {
     if (R <= 0 || n_rows <= 0) return 0;
-    if (C < 1 || bs < 1 || C % bs) return (int)cudaErrorInvalidValue;
-    const dim3 grid((C + 127) / 128, R);
+    if (C < 1 || bs < 1 || C % bs || segments < 1 || segments > GL_MAX_SEGS) return (int)cudaErrorInvalidValue;
+    const dim3 grid((C + 31) / 32, R), block(32 * segments);
     if (dtype == SS_BF16)
-        ss_launch(gated_linear_recurrence_kernel<bf16>, grid, dim3(128), 0, stream, pre, bias, (const bf16*)u, (const bf16*)y,
+        ss_launch(gated_linear_recurrence_kernel<bf16>, grid, block, 0, stream, pre, bias, (const bf16*)u, (const bf16*)y,
                   y_stride, lam, rate, state, (bf16*)out, q_start, seq_lens, slots, n_rows, C, bs, n_slots, err);
     else
-        ss_launch(gated_linear_recurrence_kernel<float>, grid, dim3(128), 0, stream, pre, bias, (const float*)u,
+        ss_launch(gated_linear_recurrence_kernel<float>, grid, block, 0, stream, pre, bias, (const float*)u,
                   (const float*)y, y_stride, lam, rate, state, (float*)out, q_start, seq_lens, slots, n_rows, C, bs, n_slots, err);
     return SS_LAUNCH_CHECK();
 }
@@ -317,7 +410,7 @@ extern "C" int ss_scaled_sum(const void* a, float sa, const void* b, float sb, v
 
 // ---------------------------------------------------------------- relu(z)^2 over the first `cols` columns of rows
 template <typename T>
-__global__ void relu_square_kernel(const T* __restrict__ in, int64_t in_stride, T* __restrict__ out, int64_t n, int cols) {
+__global__ void relu_square_kernel(const T* in, int64_t in_stride, T* out, int64_t n, int cols) {  // in may be out
     pdl_wait();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
@@ -326,11 +419,32 @@ __global__ void relu_square_kernel(const T* __restrict__ in, int64_t in_stride, 
     out[idx] = from_float<T>(z > 0.f ? z * z : 0.f);
 }
 
+// bfloat16 with columns, row stride and both addresses in steps of 8 elements: sixteen bytes a load and a store
+__global__ void relu_square_bf16x8_kernel(const bf16* in, int64_t in_stride, bf16* out, int64_t n8, int cols8) {
+    pdl_wait();
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n8) return;
+    const int64_t row = idx / cols8;
+    const uint4 raw = *reinterpret_cast<const uint4*>(in + row * in_stride + (idx - row * cols8) * 8);
+    const uint32_t q[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float lo = __uint_as_float(q[e] << 16), hi = __uint_as_float(q[e] & 0xffff0000u);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(lo > 0.f ? lo * lo : 0.f, hi > 0.f ? hi * hi : 0.f);
+        o[e] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 extern "C" int ss_relu_square(const void* in, int64_t in_stride, void* out, int n_rows, int cols, int dtype, cudaStream_t stream) {
     const int64_t n = (int64_t)n_rows * cols;
     if (n <= 0) return 0;
     const dim3 grid((unsigned)((n + 255) / 256));
-    if (dtype == SS_BF16)
+    if (dtype == SS_BF16 && cols % 8 == 0 && in_stride % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0)
+        ss_launch(relu_square_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (const bf16*)in, in_stride,
+                  (bf16*)out, n / 8, cols / 8);
+    else if (dtype == SS_BF16)
         ss_launch(relu_square_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)in, in_stride, (bf16*)out, n, cols);
     else
         ss_launch(relu_square_kernel<float>, grid, dim3(256), 0, stream, (const float*)in, in_stride, (float*)out, n, cols);

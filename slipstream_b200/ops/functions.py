@@ -97,7 +97,7 @@ _OPS_SIGNATURES = {
     "ss_gated_rmsnorm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     "ss_block_gates": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ss_gated_linear_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_head_gate": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     "ss_scaled_sum": [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int64, c_int, c_void_p],
     "ss_relu_square": [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -2005,6 +2005,9 @@ def block_gates(u: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return pre
 
 
+RECURRENCE_SEGMENTS = 16  # warps that share a request's rows of a step with prompt portions
+
+
 def gated_linear_recurrence(pre: torch.Tensor, bias: torch.Tensor | None, u: torch.Tensor, y: torch.Tensor, lam: torch.Tensor,
                             rate: float, state: torch.Tensor, ctx) -> torch.Tensor:
     """The real-gated linear recurrence over each request's tokens, continued from and left in ``state`` (float32
@@ -2012,7 +2015,8 @@ def gated_linear_recurrence(pre: torch.Tensor, bias: torch.Tensor | None, u: tor
     [N, C] the recurrence's input, ``y`` a view [N, C] (unit inner stride) of the other branch before its activation,
     ``lam`` float32 [C].  Per channel: ``r = sigmoid(pre1 + bias1)``, ``i = sigmoid(pre2 + bias2)``,
     ``a = exp(-rate r softplus(lam))``, ``S <- a S + sqrt(1 - a^2) i u``; returns ``S gelu_tanh(y)`` [N, C] in the
-    dtype of ``u``."""
+    dtype of ``u``.  In steps with prompt portions a request's rows are cut into `RECURRENCE_SEGMENTS` segments that
+    are walked side by side (``pre`` is used as scratch and holds other values afterwards)."""
     _need(pre, torch.float32, "gate pre-activations")
     _need(u, None, "u")
     _need(lam, torch.float32, "lam")
@@ -2032,7 +2036,8 @@ def gated_linear_recurrence(pre: torch.Tensor, bias: torch.Tensor | None, u: tor
                                                     lam.data_ptr(), float(rate), state.data_ptr(), out.data_ptr(),
                                                     ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
                                                     ctx.num_requests, n, c, bs, state.shape[0], _code(u.dtype),
-                                                    error_word(u.device).data_ptr(), _stream()), "gated_linear_recurrence")
+                                                    error_word(u.device).data_ptr(), _stream(),
+                                                    1 if ctx.is_decode_only else RECURRENCE_SEGMENTS), "gated_linear_recurrence")
     return out
 
 
