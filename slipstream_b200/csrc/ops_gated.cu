@@ -26,29 +26,38 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // ---------------------------------------------------------------- linear attention with a decay per head
 //
 // proj row: [q: heads * dim | k: heads * dim | v: heads * vdim | ...] (pre-activations).  Per request and head, token
-// by token:  S <- decay S + silu(k) silu(v)^T,  o = S^T silu(q).  state: float32 [slots][heads][vdim][dim];
-// out: float32 [rows][heads * vdim].  A block takes one head of one request and DA_COLS value columns; a column is
-// held by DA_LANES lanes, each with groups of four neighbouring rows of it in registers (lane s has the groups s,
-// s + DA_LANES, ...), so that q and k come from shared memory sixteen bytes a load; tokens are staged DA_BATCH at a
-// time with their activation applied, and the dot products of four tokens are reduced over the lanes together.
+// by token:  S <- decay S + silu(k) silu(v)^T,  o = S^T silu(q).  state: float32 [slots][heads][dim][vdim];
+// out: float32 [rows][heads * vdim].
+//
+// A block takes one head of one request and DA_COLS value columns.  A lane is a column; warp w holds rows
+// w RMAX .. (w + 1) RMAX - 1 of every column in registers, so that q and k are read from shared memory as broadcasts,
+// sixteen bytes a load, and nothing is exchanged between lanes: a warp leaves its part of a token's dot products in
+// shared memory, and after a batch of DA_BATCH tokens the parts are added in the order of the warps.  Tokens are
+// staged a batch at a time with their activation applied.
 // FAST (the bfloat16 rows): the activation with the approximate exponential and division, whose error is far below
-// the rounding of the projected values.
-#define DA_LANES 8
+// the rounding of the projected values.  VEC (bfloat16 rows whose sizes and addresses are in steps of 8 elements):
+// a batch's values are fetched sixteen bytes a load into registers while the batch in front is computed, so that no
+// token waits for memory; otherwise a thread has four loads in flight while it stages.
+#define DA_WARPS 8
 #define DA_COLS 32
 #define DA_BATCH 16
 #define DA_MAX_DIM 256
+#define DA_MAX_VEC 5  // 16-byte loads a thread issues for one batch: 16 * (2 * 256 / 8 + 32 / 8) / 256, rounded up
 
 template <bool FAST>
 __device__ __forceinline__ float silu_act(float z) {
     return FAST ? __fdividef(z, 1.0f + __expf(-z)) : z / (1.0f + expf(-z));
 }
 
-template <typename T, int RMAX, bool FAST>
-__global__ void __launch_bounds__(DA_LANES * DA_COLS)
+template <int RMAX>
+constexpr int da_smem_bytes() { return (2 * DA_BATCH * DA_WARPS * RMAX + DA_BATCH * DA_COLS + DA_WARPS * DA_BATCH * DA_COLS) * 4; }
+
+template <typename T, int RMAX, bool FAST, bool VEC>
+__global__ void __launch_bounds__(DA_WARPS * 32)
 decay_attention_kernel(const T* __restrict__ proj, int64_t stride, const float* __restrict__ decay, float* __restrict__ state,
                        float* __restrict__ out, const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                        const int32_t* __restrict__ slots, int heads, int dim, int vdim, int n_slots, int* err) {
-    constexpr int GROUPS = RMAX / 4;
+    constexpr int GROUPS = RMAX / 4, W = DA_WARPS * RMAX;  // W: rows of shared memory a token's q (or k) takes
     const int col_blocks = (vdim + DA_COLS - 1) / DA_COLS;
     const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks, r = blockIdx.y;
     const float d = decay[h];
@@ -60,78 +69,160 @@ decay_attention_kernel(const T* __restrict__ proj, int64_t stride, const float* 
         if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         return;
     }
-    __shared__ __align__(16) float qs[DA_BATCH][DA_MAX_DIM], ks[DA_BATCH][DA_MAX_DIM];
-    __shared__ float vs[DA_BATCH][DA_COLS];
-    const int tid = threadIdx.x, sub = tid % DA_LANES, col = tid / DA_LANES, j = cb * DA_COLS + col;
+    extern __shared__ __align__(16) float da_smem[];
+    float* qs = da_smem;                       // [DA_BATCH][W]
+    float* ks = qs + DA_BATCH * W;             // [DA_BATCH][W]
+    float* vs = ks + DA_BATCH * W;             // [DA_BATCH][DA_COLS]
+    float* red = vs + DA_BATCH * DA_COLS;      // [DA_WARPS][DA_BATCH][DA_COLS]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j = cb * DA_COLS + lane;
     const bool live = j < vdim;
-    const int dim4 = (dim + 3) & ~3;  // rows behind the head's last one are zeros in shared memory
-    float* sp = state + (((int64_t)slot * heads + h) * vdim + (live ? j : 0)) * dim;
+    const int row0 = warp * RMAX;
+    if (dim < W)  // rows behind the head's last one stay zero
+        for (int i = tid; i < 2 * DA_BATCH * (W - dim); i += blockDim.x) qs[(i / (W - dim)) * W + dim + i % (W - dim)] = 0.f;
+    float* sp = state + ((int64_t)slot * heads + h) * dim * vdim + (live ? j : 0);  // a row's columns lie side by side
     float S[RMAX];
 #pragma unroll
-    for (int g = 0; g < GROUPS; ++g)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int row = 4 * (sub + g * DA_LANES) + e;
-            S[4 * g + e] = (live && row < dim) ? sp[row] : 0.f;
-        }
+    for (int i = 0; i < RMAX; ++i) S[i] = (live && row0 + i < dim) ? sp[(int64_t)(row0 + i) * vdim] : 0.f;
     const int64_t k_off = (int64_t)heads * dim + (int64_t)h * dim, v_off = 2 * (int64_t)heads * dim + (int64_t)h * vdim;
+    // VEC: the items of a batch are 16-byte pieces, per token dim / 8 of q, dim / 8 of k and DA_COLS / 8 of v
+    const int dim8 = dim >> 3, ipt = 2 * dim8 + DA_COLS / 8;
+    uint4 raw[DA_MAX_VEC];
+    auto issue = [&](int t0, int nb) {
+#pragma unroll
+        for (int w = 0; w < DA_MAX_VEC; ++w) {
+            const int i = tid + w * DA_WARPS * 32;
+            raw[w] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < nb * ipt) {
+                const int t = i / ipt, c = i - t * ipt;
+                const bf16* row = reinterpret_cast<const bf16*>(proj) + (int64_t)(q0 + t0 + t) * stride;
+                const bf16* src = c < dim8 ? row + (int64_t)h * dim + c * 8
+                                : c < 2 * dim8 ? row + k_off + (c - dim8) * 8 : row + v_off + cb * DA_COLS + (c - 2 * dim8) * 8;
+                if (c < 2 * dim8 || cb * DA_COLS + (c - 2 * dim8) * 8 < vdim) raw[w] = *reinterpret_cast<const uint4*>(src);
+            }
+        }
+    };
+    auto deposit = [&](int nb) {
+#pragma unroll
+        for (int w = 0; w < DA_MAX_VEC; ++w) {
+            const int i = tid + w * DA_WARPS * 32;
+            if (i < nb * ipt) {
+                const int t = i / ipt, c = i - t * ipt;
+                float* dst = c < dim8 ? qs + t * W + c * 8 : c < 2 * dim8 ? ks + t * W + (c - dim8) * 8 : vs + t * DA_COLS + (c - 2 * dim8) * 8;
+                const uint32_t q[4] = {raw[w].x, raw[w].y, raw[w].z, raw[w].w};
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    f[2 * e] = silu_act<FAST>(__uint_as_float(q[e] << 16));
+                    f[2 * e + 1] = silu_act<FAST>(__uint_as_float(q[e] & 0xffff0000u));
+                }
+                *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            }
+        }
+    };
+    if (VEC) issue(0, min(DA_BATCH, q_len));
     for (int t0 = 0; t0 < q_len; t0 += DA_BATCH) {
         const int nb = min(DA_BATCH, q_len - t0);
-        __syncthreads();
-        for (int i = tid; i < nb * dim4; i += blockDim.x) {
-            const int t = i / dim4, e = i - t * dim4;
-            const T* row = proj + (int64_t)(q0 + t0 + t) * stride;
-            qs[t][e] = e < dim ? silu_act<FAST>(to_float(row[(int64_t)h * dim + e])) : 0.f;
-            ks[t][e] = e < dim ? silu_act<FAST>(to_float(row[k_off + e])) : 0.f;
-        }
-        for (int i = tid; i < nb * DA_COLS; i += blockDim.x) {
-            const int t = i / DA_COLS, e = i - t * DA_COLS;
-            vs[t][e] = cb * DA_COLS + e < vdim ? silu_act<FAST>(to_float(proj[(int64_t)(q0 + t0 + t) * stride + v_off + cb * DA_COLS + e])) : 0.f;
-        }
-        __syncthreads();
-        for (int t = 0; t < nb; t += 4) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        __syncthreads();  // the batch in front is done with shared memory (and, the first time, the zeros are in place)
+        if (VEC) {
+            deposit(nb);
+            __syncthreads();
+            if (t0 + DA_BATCH < q_len) issue(t0 + DA_BATCH, min(DA_BATCH, q_len - t0 - DA_BATCH));  // in flight while this batch is computed
+        } else {
+            const int n_qk = nb * dim, n_all = n_qk + nb * DA_COLS;
+            for (int i0 = tid; i0 < n_all; i0 += 4 * blockDim.x) {  // four loads (pairs, for q and k) in flight
+                float a[4], b[4];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                if (t + w >= nb) break;
-                const float v = vs[t + w][col];
+                for (int w = 0; w < 4; ++w) {
+                    const int i = i0 + w * blockDim.x;
+                    a[w] = b[w] = 0.f;
+                    if (i < n_qk) {
+                        const int t = i / dim, e = i - t * dim;
+                        const T* row = proj + (int64_t)(q0 + t0 + t) * stride;
+                        a[w] = to_float(row[(int64_t)h * dim + e]);
+                        b[w] = to_float(row[k_off + e]);
+                    } else if (i < n_all) {
+                        const int t = (i - n_qk) / DA_COLS, e = (i - n_qk) - t * DA_COLS;
+                        if (cb * DA_COLS + e < vdim) a[w] = to_float(proj[(int64_t)(q0 + t0 + t) * stride + v_off + cb * DA_COLS + e]);
+                    }
+                }
 #pragma unroll
-                for (int g = 0; g < GROUPS; ++g) {
-                    const int at = 4 * (sub + g * DA_LANES);
-                    if (at < dim4) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(&ks[t + w][at]);
-                        const float4 q4 = *reinterpret_cast<const float4*>(&qs[t + w][at]);
-                        S[4 * g + 0] = fmaf(k4.x, v, d * S[4 * g + 0]);
-                        S[4 * g + 1] = fmaf(k4.y, v, d * S[4 * g + 1]);
-                        S[4 * g + 2] = fmaf(k4.z, v, d * S[4 * g + 2]);
-                        S[4 * g + 3] = fmaf(k4.w, v, d * S[4 * g + 3]);
-                        acc[w] = fmaf(S[4 * g + 0], q4.x, acc[w]);
-                        acc[w] = fmaf(S[4 * g + 1], q4.y, acc[w]);
-                        acc[w] = fmaf(S[4 * g + 2], q4.z, acc[w]);
-                        acc[w] = fmaf(S[4 * g + 3], q4.w, acc[w]);
+                for (int w = 0; w < 4; ++w) {
+                    const int i = i0 + w * blockDim.x;
+                    if (i < n_qk) {
+                        const int t = i / dim, e = i - t * dim;
+                        qs[t * W + e] = silu_act<FAST>(a[w]);
+                        ks[t * W + e] = silu_act<FAST>(b[w]);
+                    } else if (i < n_all) {
+                        const int t = (i - n_qk) / DA_COLS, e = (i - n_qk) - t * DA_COLS;
+                        vs[t * DA_COLS + e] = silu_act<FAST>(a[w]);  // silu(0) = 0 behind the last column
                     }
                 }
             }
+            __syncthreads();
+        }
+        if (row0 < dim) {  // (a warp whose rows lie behind the head's last one has nothing to add)
+            for (int t = 0; t < nb; t += 2) {  // two tokens' loads in flight; their updates in order
+                const int t1 = min(t + 1, nb - 1);
+                const float v0 = vs[t * DA_COLS + lane], v1 = vs[t1 * DA_COLS + lane];
+                float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-            for (int o = DA_LANES / 2; o > 0; o >>= 1)
-#pragma unroll
-                for (int w = 0; w < 4; ++w) acc[w] += __shfl_xor_sync(0xffffffffu, acc[w], o);
-            if (sub == 0 && live) {
-#pragma unroll
-                for (int w = 0; w < 4; ++w)
-                    if (t + w < nb) out[(int64_t)(q0 + t0 + t + w) * heads * vdim + (int64_t)h * vdim + j] = acc[w];
+                for (int g = 0; g < GROUPS; ++g) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + t * W + row0 + 4 * g);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + t * W + row0 + 4 * g);
+                    const float4 k5 = *reinterpret_cast<const float4*>(ks + t1 * W + row0 + 4 * g);
+                    const float4 q5 = *reinterpret_cast<const float4*>(qs + t1 * W + row0 + 4 * g);
+                    S[4 * g + 0] = fmaf(k4.x, v0, d * S[4 * g + 0]);
+                    S[4 * g + 1] = fmaf(k4.y, v0, d * S[4 * g + 1]);
+                    S[4 * g + 2] = fmaf(k4.z, v0, d * S[4 * g + 2]);
+                    S[4 * g + 3] = fmaf(k4.w, v0, d * S[4 * g + 3]);
+                    a0 = fmaf(S[4 * g + 0], q4.x, a0);
+                    a1 = fmaf(S[4 * g + 1], q4.y, a1);
+                    a0 = fmaf(S[4 * g + 2], q4.z, a0);
+                    a1 = fmaf(S[4 * g + 3], q4.w, a1);
+                    if (t + 1 < nb) {
+                        S[4 * g + 0] = fmaf(k5.x, v1, d * S[4 * g + 0]);
+                        S[4 * g + 1] = fmaf(k5.y, v1, d * S[4 * g + 1]);
+                        S[4 * g + 2] = fmaf(k5.z, v1, d * S[4 * g + 2]);
+                        S[4 * g + 3] = fmaf(k5.w, v1, d * S[4 * g + 3]);
+                        b0 = fmaf(S[4 * g + 0], q5.x, b0);
+                        b1 = fmaf(S[4 * g + 1], q5.y, b1);
+                        b0 = fmaf(S[4 * g + 2], q5.z, b0);
+                        b1 = fmaf(S[4 * g + 3], q5.w, b1);
+                    }
+                }
+                red[(warp * DA_BATCH + t) * DA_COLS + lane] = a0 + a1;
+                if (t + 1 < nb) red[(warp * DA_BATCH + t + 1) * DA_COLS + lane] = b0 + b1;
             }
+        }
+        __syncthreads();
+        const int n_warps = min(DA_WARPS, (dim + RMAX - 1) / RMAX);  // warps that hold rows of the head
+        for (int i = tid; i < nb * DA_COLS; i += blockDim.x) {
+            const int t = i / DA_COLS, c = i - t * DA_COLS;
+            if (cb * DA_COLS + c >= vdim) continue;
+            float sum = 0.f;
+            for (int w = 0; w < n_warps; ++w) sum += red[(w * DA_BATCH + t) * DA_COLS + c];
+            out[(int64_t)(q0 + t0 + t) * heads * vdim + (int64_t)h * vdim + cb * DA_COLS + c] = sum;
         }
     }
     if (live) {
 #pragma unroll
-        for (int g = 0; g < GROUPS; ++g)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int row = 4 * (sub + g * DA_LANES) + e;
-                if (row < dim) sp[row] = S[4 * g + e];
-            }
+        for (int i = 0; i < RMAX; ++i)
+            if (row0 + i < dim) sp[(int64_t)(row0 + i) * vdim] = S[i];
     }
+}
+
+template <typename T, int RMAX, bool FAST, bool VEC>
+static int launch_decay_attention(const void* proj, int64_t stride, const float* decay, float* state, float* out,
+                                  const int32_t* q_start, const int32_t* seq_lens, const int32_t* slots, int R, int heads,
+                                  int dim, int vdim, int n_slots, int* err, cudaStream_t stream) {
+    constexpr int smem = da_smem_bytes<RMAX>();
+    static SsPerDevice opted;
+    if (int rc = ss_opt_in_smem(decay_attention_kernel<T, RMAX, FAST, VEC>, smem, opted)) return rc;
+    const dim3 grid(heads * ((vdim + DA_COLS - 1) / DA_COLS), R), block(DA_WARPS * 32);
+    ss_launch(decay_attention_kernel<T, RMAX, FAST, VEC>, grid, block, smem, stream, (const T*)proj, stride, decay, state, out,
+              q_start, seq_lens, slots, heads, dim, vdim, n_slots, err);
+    return SS_LAUNCH_CHECK();
 }
 
 extern "C" int ss_decay_attention(const void* proj, int64_t stride, const float* decay, float* state, float* out,
@@ -139,20 +230,24 @@ extern "C" int ss_decay_attention(const void* proj, int64_t stride, const float*
                                   int dim, int vdim, int n_slots, int dtype, int* err, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (heads < 1 || dim < 1 || dim > DA_MAX_DIM || vdim < 1) return (int)cudaErrorInvalidValue;
-    const dim3 grid(heads * ((vdim + DA_COLS - 1) / DA_COLS), R), block(DA_LANES * DA_COLS);
-#define DA_GO(T, RMAX, FAST)                                                                                              \
-    ss_launch(decay_attention_kernel<T, RMAX, FAST>, grid, block, 0, stream, (const T*)proj, stride, decay, state, out,    \
-              q_start, seq_lens, slots, heads, dim, vdim, n_slots, err)
-#define DA_PICK(T, FAST)                                                                                                \
+#define DA_GO(T, RMAX, FAST, VEC)                                                                                         \
+    return launch_decay_attention<T, RMAX, FAST, VEC>(proj, stride, decay, state, out, q_start, seq_lens, slots, R, heads, \
+                                                      dim, vdim, n_slots, err, stream)
+#define DA_PICK(T, FAST, VEC)                                                                                           \
     do {                                                                                                                \
-        if (dim <= 8 * DA_LANES) DA_GO(T, 8, FAST);                                                                     \
-        else if (dim <= 16 * DA_LANES) DA_GO(T, 16, FAST);                                                              \
-        else DA_GO(T, 32, FAST);                                                                                        \
+        if (dim <= 8 * DA_WARPS) DA_GO(T, 8, FAST, VEC);                                                                \
+        else if (dim <= 16 * DA_WARPS) DA_GO(T, 16, FAST, VEC);                                                         \
+        else DA_GO(T, 32, FAST, VEC);                                                                                   \
     } while (0)
-    if (dtype == SS_BF16) DA_PICK(bf16, true); else DA_PICK(float, false);
+    const bool vec = dtype == SS_BF16 && dim % 8 == 0 && vdim % 8 == 0 && stride % 8 == 0 && ((uintptr_t)proj & 15) == 0;
+    if (dtype == SS_BF16) {
+        if (vec) DA_PICK(bf16, true, true); else DA_PICK(bf16, true, false);
+    } else {
+        DA_PICK(float, false, false);
+    }
 #undef DA_PICK
 #undef DA_GO
-    return SS_LAUNCH_CHECK();
+    return 0;
 }
 
 // ---------------------------------------------------------------- RMS norm of a row under a sigmoid gate

@@ -1949,7 +1949,7 @@ def head_product(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.
 def decay_attention(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx, heads: int, dim: int,
                     value_dim: int) -> torch.Tensor:
     """Linear attention with a fixed decay per head over each request's tokens, continued from and left in ``state``
-    (float32 [slots, heads, value_dim, dim]).  A row of ``proj`` starts with the heads' queries, then keys (``dim``
+    (float32 [slots, heads, dim, value_dim]).  A row of ``proj`` starts with the heads' queries, then keys (``dim``
     each), then values (``value_dim``), all before their activation; whatever follows is left alone.  Per head h, token
     by token: ``S <- decay[h] S + silu(k) silu(v)^T``, ``o = S^T silu(q)``.  Returns o float32 [N, heads * value_dim]."""
     _need(proj, None, "projected rows")
@@ -1958,8 +1958,8 @@ def decay_attention(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor
     n = proj.shape[0]
     if proj.shape[1] < heads * (2 * dim + value_dim) or decay.numel() != heads or not 1 <= dim <= 256:
         raise KernelError("decay_attention: the rows are narrower than their heads, or sizes out of range")
-    if tuple(state.shape[1:]) != (heads, value_dim, dim):
-        raise KernelError("decay_attention: the state must be [slots, heads, value_dim, dim]")
+    if tuple(state.shape[1:]) != (heads, dim, value_dim):
+        raise KernelError("decay_attention: the state must be [slots, heads, dim, value_dim]")
     out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=proj.device)
     _check(ops_library().ss_decay_attention(proj.data_ptr(), proj.stride(0), decay.data_ptr(), state.data_ptr(),
                                             out.data_ptr(), ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(),

@@ -214,7 +214,7 @@ class DecayedLinearAttention(Mixer):
                 WeightSpec(n["norm"], (h * v,), kind="vector", init=("one_plus_normal", 0.1))]
 
     def state_specs(self) -> list[StateSpec]:
-        return [StateSpec("memory", (self.heads, self.value_dim, self.dim))]  # S, a value column after the other
+        return [StateSpec("memory", (self.heads, self.dim, self.value_dim))]  # S, row by row
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)

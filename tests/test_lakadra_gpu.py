@@ -353,7 +353,7 @@ def test_model_structure_follows_the_configuration():
     # two pools of pages: the latent rows (layer 4 reads what layer 2 writes) and the windowed keys of layer 0
     assert [(g.spec.num_kv_heads, g.spec.head_dim, g.spec.window, g.num_entries) for g in model.group_layouts] == [(2, 32, 9, 1), (1, 48, None, 1)]
     assert [[(s.name, tuple(s.shape)) for s in entry] for entry in model.entry_state] == [
-        [("right.conv", (2, 48)), ("right.cell", (48,))], [("memory", (3, 40, 24))], [], [("memory", (2, 8, 8))], []]
+        [("right.conv", (2, 48)), ("right.cell", (48,))], [("memory", (3, 24, 40))], [], [("memory", (2, 8, 8))], []]
 
 
 # --------------------------------------------------------------------------- every mechanism alone
@@ -379,7 +379,7 @@ def test_decayed_linear_attention_whole_and_cut_with_slots_used_again(heads, dim
              "p.g": eye(heads * (2 * dim + vdim), heads * vdim), "p.norm": weight.double(), "p.o": torch.eye(heads * vdim, dtype=F64)}
         want[k] = plain.lightning(m, w, "p", x, 1e-6)
     for plan in PLANS:
-        state = torch.randn(3, heads, vdim, dim, device=DEV)  # what a slot's last owner left
+        state = torch.randn(3, heads, dim, vdim, device=DEV)  # what a slot's last owner left
         state[[0, 2]] = 0.0  # the engine clears a slot at admission
 
         def run(x, ctx):
