@@ -684,24 +684,54 @@ extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t d
 // experts' ride along in the product: their logits leave raw in extra_out[token][extra] (a gate that reads the
 // same input, say).  A block per token.
 #define ROUTER_MAX_EXPERTS 1024
+#define ROUTER_THREADS 256
+// A lane's part of w . x (x in shared memory as float32).  bfloat16 rows of a length in steps of 8 (their starts are
+// then on 16-byte boundaries when the matrix is): sixteen bytes a load, four loads in flight.
+__device__ __forceinline__ float router_dot(const float* __restrict__ w, const float* __restrict__ xs, int hidden, int lane) {
+    float acc = 0.f;
+    for (int i = lane; i < hidden; i += 32) acc = fmaf(w[i], xs[i], acc);
+    return acc;
+}
+__device__ __forceinline__ float router_dot(const bf16* __restrict__ w, const float* __restrict__ xs, int hidden, int lane) {
+    float acc = 0.f;
+    if ((hidden & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+#pragma unroll 4
+        for (int i = lane * 8; i < hidden; i += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+            const float4 a = *reinterpret_cast<const float4*>(xs + i), b = *reinterpret_cast<const float4*>(xs + i + 4);
+            acc = fmaf(__uint_as_float(raw.x << 16), a.x, acc);
+            acc = fmaf(__uint_as_float(raw.x & 0xffff0000u), a.y, acc);
+            acc = fmaf(__uint_as_float(raw.y << 16), a.z, acc);
+            acc = fmaf(__uint_as_float(raw.y & 0xffff0000u), a.w, acc);
+            acc = fmaf(__uint_as_float(raw.z << 16), b.x, acc);
+            acc = fmaf(__uint_as_float(raw.z & 0xffff0000u), b.y, acc);
+            acc = fmaf(__uint_as_float(raw.w << 16), b.z, acc);
+            acc = fmaf(__uint_as_float(raw.w & 0xffff0000u), b.w, acc);
+        }
+        return acc;
+    }
+    for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(w[i]), xs[i], acc);
+    return acc;
+}
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(ROUTER_THREADS)
 router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* __restrict__ ids,
               float* __restrict__ weights, int hidden, int experts, int top, int renormalize, int softmax,
               const float* __restrict__ correction, int groups, int keep, float* __restrict__ extra_out, int extra) {
     pdl_wait();
-    extern __shared__ float rsm[];
-    float* xs = rsm;                  // [hidden]
-    float* z = rsm + hidden;          // [experts] scores
+    extern __shared__ __align__(16) float rsm[];
+    float* xs = rsm;                  // [hidden] (rounded up to a multiple of 4)
+    float* z = rsm + ((hidden + 3) & ~3);  // [experts] scores
     float* c = z + experts;           // [experts] choice scores
     float* gb = c + experts;          // [groups] the groups' scores
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < hidden; i += blockDim.x) xs[i] = to_float(x[(int64_t)t * hidden + i]);
     __syncthreads();
-    for (int e = warp; e < experts + extra; e += 4) {
+    const int n_warps = blockDim.x >> 5;
+    for (int e = warp; e < experts + extra; e += n_warps) {
         const T* w = w_router + (int64_t)e * hidden;
-        float acc = 0.f;
-        for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(w[i]), xs[i], acc);
+        float acc = router_dot(w, xs, hidden, lane);
         acc = warp_sum(acc);
         if (lane == 0) {
             if (e >= experts) extra_out[(int64_t)t * extra + (e - experts)] = acc;
@@ -789,13 +819,13 @@ extern "C" int ss_router(const void* x, const void* w_router, int32_t* ids, floa
     if (experts < 1 || experts > ROUTER_MAX_EXPERTS || top < 1 || top > experts) return (int)cudaErrorInvalidValue;
     if (groups < 1 || experts % groups || keep < 1 || keep > groups || extra < 0 || (extra > 0 && !extra_out))
         return (int)cudaErrorInvalidValue;
-    const int smem = (hidden + 2 * experts + groups) * 4;
+    const int smem = (((hidden + 3) & ~3) + 2 * experts + groups) * 4;
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     if (dtype == SS_BF16)
-        ss_launch(router_kernel<bf16>, dim3(n_tokens), dim3(128), smem, stream, (const bf16*)x, (const bf16*)w_router, ids,
+        ss_launch(router_kernel<bf16>, dim3(n_tokens), dim3(ROUTER_THREADS), smem, stream, (const bf16*)x, (const bf16*)w_router, ids,
                   weights, hidden, experts, top, renormalize, softmax, correction, groups, keep, extra_out, extra);
     else
-        ss_launch(router_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)x, (const float*)w_router,
+        ss_launch(router_kernel<float>, dim3(n_tokens), dim3(ROUTER_THREADS), smem, stream, (const float*)x, (const float*)w_router,
                   ids, weights, hidden, experts, top, renormalize, softmax, correction, groups, keep, extra_out, extra);
     return SS_LAUNCH_CHECK();
 }

@@ -1562,7 +1562,7 @@ def router(x: torch.Tensor, weight: torch.Tensor, top: int, renormalize: bool = 
     n, hidden = x.shape
     experts = weight.shape[0] - int(extra)
     if (weight.shape[1] != hidden or not 1 <= top <= experts or experts > 1024 or extra < 0
-            or (hidden + 2 * experts + groups) * 4 > 48 * 1024):
+            or (hidden + 3 + 2 * experts + groups) * 4 > 48 * 1024):
         raise KernelError("router: sizes out of range")
     if groups < 1 or experts % groups or not 1 <= keep <= groups or top > keep * (experts // groups):
         raise KernelError("router: the experts do not split into such groups, or too few are kept for the choices")

@@ -92,6 +92,12 @@ def configs():
                          layer(lightning(2, 40, 24, (0.9, 0.999)), None),
                          layer(pair(3, 1, 48, 80, 0.7, 3, 100.0, 8, 2.0, 40, 5, 1, 1.5, 0.5), moe(40, 4, 2, 4, (4, 1), 16)),
                          layer(latent(3, 8, 24, 32, 24, 24, 0.8, 1.0e6), moe(8, 2, 2))]},
+        # pairs only, with heads of the sizes the tcgen05 attention kernels take (64 and 128) under windows of 20 and 40
+        # with the unit sink, grouped heads, and a layer without feed-forward between
+        "D": {"architecture": "Lakadra", "vocab": 120, "width": 64, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+              "layers": [layer(pair(4, 2, 64, 64, 0.4, 20, 3000.0, 32, 2.0, 32, 2, 4, 1.1, 0.7), moe(16, 3, 2, 1, (2, 1), 24)),
+                         layer(pair(2, 1, 128, 128, 0.3, 40, 1.0e5, 128, None, 24, 1, 3, 0.9, 1.2), None),
+                         layer(lightning(2, 32, 64, (0.9, 0.99)), moe(16, 3, 2, 1, (2, 1), 24))]},
     }
 
 
@@ -530,7 +536,7 @@ def test_small_kernels(dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cut_and_batch_gives_the_plain_logits(models, name, dtype):
     """Whole prompts; token by token; portions of several sizes down to two tokens; three unequal requests mixed, in a
     pool smaller than their sum, with two state slots, so that pages and slots are used again."""
@@ -642,10 +648,12 @@ def test_a_state_slot_that_is_not_cleared_shows(models):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_portions_that_take_the_tensor_core_paths(models, dtype):
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_portions_that_take_the_tensor_core_paths(models, name, dtype):
     """600-token portions: the library's batched product for the gates, mma.sync tiles of 128 rows and (from 1,024
-    pairs) the grouped tcgen05 kernel for the experts, the tcgen05 prefill attention with a unit sink (model B)."""
-    folder, config, weights, key = model_for(models, "B", dtype)
+    pairs) the grouped tcgen05 kernel for the experts, the tcgen05 prefill attention with a unit sink (model B), and
+    with a unit sink under a sliding window (model D)."""
+    folder, config, weights, key = model_for(models, name, dtype)
     toks = tokens_of(config["vocab"], 640, 77)
     want = plain_logits(key, config, weights, toks)
     runner = make_runner(folder, dtype, pages=44, seqs=1)
