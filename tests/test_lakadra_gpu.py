@@ -558,6 +558,82 @@ def test_every_cut_and_batch_gives_the_plain_logits(models, name, dtype):
             assert close(logits, want[k][: logits.shape[0]], dtype), (what, k, distance(logits, want[k][: logits.shape[0]]))
 
 
+def drawn_config(seed):
+    """A model of this design drawn at random: sizes, head counts, the order of the layers, windows, constants and which
+    options are present all follow the seed."""
+    import random
+    rnd = random.Random(seed)
+    width = rnd.choice([40, 48, 56, 72, 88, 104, 136])
+    n_layers = rnd.randint(3, 6)
+    own_latents, layers = [], []
+    for i in range(n_layers):
+        kind = rnd.choice(["lightning", "latent_attention", "parallel"])
+        if kind == "lightning":
+            heads = rnd.randint(1, 4)
+            mixer = lightning(heads, rnd.randint(3, 72), rnd.randint(3, 72), [round(rnd.uniform(0.3, 0.999), 4) for _ in range(heads)])
+        elif kind == "latent_attention":
+            if own_latents and rnd.random() < 0.45:
+                j = rnd.choice(own_latents)
+                src = layers[j]["mixer"]
+                mixer = latent(rnd.randint(1, 5), rnd.randint(2, 40), src["rot_dim"], rnd.randint(2, 40), rnd.randint(8, 48), src["kv_rank"],
+                               round(rnd.uniform(0.3, 1.0), 3), src["rot"]["base"], kv_from=j)
+            else:
+                own_latents.append(i)
+                mixer = latent(rnd.randint(1, 5), rnd.randint(2, 40), 2 * rnd.randint(1, 10), rnd.randint(2, 40), rnd.randint(8, 48),
+                               rnd.randint(8, 60), round(rnd.uniform(0.3, 1.0), 3), rnd.choice([100.0, 10000.0, 5.0e5]))
+        else:
+            kv = rnd.randint(1, 3)
+            dim = 2 * rnd.randint(4, 36)
+            blocks = rnd.randint(1, 4)
+            mixer = pair(kv * rnd.randint(1, 3), kv, dim, rnd.randint(3, 72), round(rnd.uniform(0.3, 0.9), 3),
+                         rnd.choice([None, rnd.randint(2, 45)]), rnd.choice([50.0, 10000.0, 1.0e6]), 2 * rnd.randint(1, dim // 2),
+                         rnd.choice([None, 2.0, 8.0]), blocks * rnd.randint(3, 30), blocks, rnd.randint(1, 5),
+                         round(rnd.uniform(0.5, 1.5), 2), round(rnd.uniform(0.5, 1.5), 2))
+        mlp = None
+        if rnd.random() < 0.8:
+            experts, identity = rnd.randint(1, 6), rnd.randint(0, 3)
+            slots = experts + identity
+            groups = None
+            counts = [c for c in range(2, slots + 1) if slots % c == 0]
+            if counts and rnd.random() < 0.6:
+                count = rnd.choice(counts)
+                groups = (count, rnd.randint(1, count))
+            room = groups[1] * (slots // groups[0]) if groups else slots
+            mlp = moe(rnd.randint(4, 40), experts, rnd.randint(1, room), identity, groups, rnd.choice([None, rnd.randint(4, 40)]))
+        layers.append(layer(mixer, mlp))
+    config = {"architecture": "Lakadra", "vocab": rnd.randint(60, 200), "width": width, "norm": {"eps": rnd.choice([1e-6, 1e-5])},
+              "layers": layers}
+    if rnd.random() < 0.7:
+        config["logit_scale"] = round(rnd.uniform(0.5, 2.5), 2)
+    if rnd.random() < 0.7:
+        config["logit_softcap"] = round(rnd.uniform(5.0, 40.0), 1)
+    return config
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_models_drawn_at_random(tmp_path, seed, dtype):
+    """Six models whose every size, constant and option follows a seed: whole prompts, and portions beside decoded tokens
+    under a pool smaller than the requests with two state slots."""
+    from slipstream_b200.config.lakadra_config import LakadraConfig
+    config = drawn_config(seed)
+    LakadraConfig.from_dict(config)  # the draw is a model the reader takes
+    if dtype == "bfloat16":
+        config = cooled(config)
+    weights = write_model(tmp_path / "m", config, 40 + seed, heat=1.0 if dtype == "float32" else 0.3)
+    vocab = config["vocab"]
+    reqs = {"a": tokens_of(vocab, 60, seed), "b": tokens_of(vocab, 23, seed + 100), "c": tokens_of(vocab, 41, seed + 200)}
+    want = {k: plain.forward(config, weights, t) for k, t in reqs.items()}
+    plans = {"whole": [[("a", 60)], [("b", 23)], [("c", 41)]],
+             "mixed": [[("a", 19), ("b", 2)], [("a", 1), ("b", 20)], [("a", 38), ("b", 1)], [("a", 2), ("c", 3)], [("c", 1)], [("c", 37)]]}
+    for what, plan in plans.items():
+        runner = make_runner(str(tmp_path / "m"), dtype, pages=6, seqs=2)
+        got = replay(runner, reqs, plan)
+        for k, logits in got.items():
+            assert close(logits, want[k][: logits.shape[0]], dtype), (seed, what, k, distance(logits, want[k][: logits.shape[0]]))
+
+
 @pytest.mark.gpu
 def test_the_stream_after_every_layer(models):
     from slipstream_b200.engine.context import plan_step, to_device
