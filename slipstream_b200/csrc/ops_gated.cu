@@ -29,7 +29,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // by token:  S <- decay S + silu(k) silu(v)^T,  o = S^T silu(q).  state: float32 [slots][heads][dim][vdim];
 // out: float32 [rows][heads * vdim].
 //
-// A block takes one head of one request and DA_COLS value columns.  A lane is a column; warp w holds rows
+// A block of DA_WARPS warps takes one head of one request and DA_COLS value columns.  A lane is a column; warp w holds rows
 // w RMAX .. (w + 1) RMAX - 1 of every column in registers, so that q and k are read from shared memory as broadcasts,
 // sixteen bytes a load, and nothing is exchanged between lanes: a warp leaves its part of a token's dot products in
 // shared memory, and after a batch of DA_BATCH tokens the parts are added in the order of the warps.  Tokens are
@@ -38,11 +38,11 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // the rounding of the projected values.  VEC (bfloat16 rows whose sizes and addresses are in steps of 8 elements):
 // a batch's values are fetched sixteen bytes a load into registers while the batch in front is computed, so that no
 // token waits for memory; otherwise a thread has four loads in flight while it stages.
-#define DA_WARPS 8
+#define DA_WARPS 16
 #define DA_COLS 32
 #define DA_BATCH 16
 #define DA_MAX_DIM 256
-#define DA_MAX_VEC 5  // 16-byte loads a thread issues for one batch: 16 * (2 * 256 / 8 + 32 / 8) / 256, rounded up
+#define DA_MAX_VEC 3  // 16-byte loads a thread issues for one batch: 16 * (2 * 256 / 8 + 32 / 8) / 512, rounded up
 
 template <bool FAST>
 __device__ __forceinline__ float silu_act(float z) {
@@ -235,9 +235,9 @@ extern "C" int ss_decay_attention(const void* proj, int64_t stride, const float*
                                                       dim, vdim, n_slots, err, stream)
 #define DA_PICK(T, FAST, VEC)                                                                                           \
     do {                                                                                                                \
-        if (dim <= 8 * DA_WARPS) DA_GO(T, 8, FAST, VEC);                                                                \
-        else if (dim <= 16 * DA_WARPS) DA_GO(T, 16, FAST, VEC);                                                         \
-        else DA_GO(T, 32, FAST, VEC);                                                                                   \
+        if (dim <= 4 * DA_WARPS) DA_GO(T, 4, FAST, VEC);                                                                \
+        else if (dim <= 8 * DA_WARPS) DA_GO(T, 8, FAST, VEC);                                                           \
+        else DA_GO(T, 16, FAST, VEC);                                                                                   \
     } while (0)
     const bool vec = dtype == SS_BF16 && dim % 8 == 0 && vdim % 8 == 0 && stride % 8 == 0 && ((uintptr_t)proj & 15) == 0;
     if (dtype == SS_BF16) {
