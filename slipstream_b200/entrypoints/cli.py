@@ -19,7 +19,7 @@ import sys
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="slipstream_b200", description="Qwen2.5 generation on one B200")
+    p = argparse.ArgumentParser(prog="slipstream_b200", description="generation with any registered decoder on one B200")
     p.add_argument("--model", required=True, help="folder with config.json and safetensors weights")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default=None)
     p.add_argument("--max-model-len", type=int, default=None)
